@@ -1,0 +1,193 @@
+// extern "C" boundary of libb200mla.so: argument validation, workspace layout, kernel selection
+// and launches.  Declarations and the reference interfaces they replace: include/b200_mla.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/b200_mla.h"
+#include "mla_common.cuh"
+
+namespace b200mla {
+cudaError_t launch_generic(const MlaParams& p, cudaStream_t stream);
+size_t generic_smem_bytes(int batch);
+cudaError_t launch_sm100(const MlaParams& p, cudaStream_t stream);
+bool sm100_supported(const MlaParams& p);
+int sm100_rows_per_cta(const MlaParams& p);
+cudaError_t launch_combine_spans(const MlaParams& p, cudaStream_t stream);
+cudaError_t launch_combine_parts(const float* o_parts, const float* lse_parts, int parts, long long rows,
+                                 __nv_bfloat16* out, float* out_lse, cudaStream_t stream);
+cudaError_t launch_quantize_fp8(const __nv_bfloat16* x, long long n, uint8_t* out, float* scale_out,
+                                unsigned int* scratch, cudaStream_t stream);
+}  // namespace b200mla
+
+using namespace b200mla;
+
+namespace {
+
+thread_local char g_err[512] = "";
+thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int sm_count() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached = n;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+constexpr int kMaxCtasPerSm = 2;
+inline long long align256(long long x) { return (x + 255) & ~255LL; }
+
+struct WsLayout { long long prefix_off, lse_off, o_off, total; };
+
+WsLayout ws_layout(int batch, int rows, int g_max) {
+    WsLayout L;
+    const long long slots = (long long)g_max + batch;
+    L.prefix_off = 0;
+    L.lse_off = align256((long long)(batch + 1) * 4);
+    L.o_off = L.lse_off + align256(slots * rows * 4);
+    L.total = L.o_off + align256(slots * rows * (long long)V_DIM * 4);
+    return L;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t b200_mla_version(void) { return 1000; }
+
+const char* b200_mla_last_error(void) { return g_err; }
+
+int64_t b200_mla_workspace_bytes(int32_t batch, int32_t heads, int32_t q_len) {
+    if (batch <= 0 || heads <= 0 || q_len <= 0) return 0;
+    return ws_layout(batch, heads * q_len, kMaxCtasPerSm * sm_count()).total;
+}
+
+int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!a) return fail(B200_MLA_ERR_INVALID_ARG, "args is NULL");
+    if (a->batch <= 0 || a->heads <= 0 || a->q_len <= 0)
+        return fail(B200_MLA_ERR_INVALID_ARG, "batch/heads/q_len must be positive (got %d/%d/%d)", a->batch, a->heads, a->q_len);
+    if (a->batch > MAX_BATCH) return fail(B200_MLA_ERR_TOO_LARGE, "batch %d exceeds %d", a->batch, MAX_BATCH);
+    if (a->heads % 16 != 0) return fail(B200_MLA_ERR_UNSUPPORTED, "heads must be a multiple of 16 (got %d)", a->heads);
+    if (a->q_len > 8) return fail(B200_MLA_ERR_UNSUPPORTED, "q_len > 8 is not a decode shape (got %d)", a->q_len);
+    if (a->q_format != B200_MLA_Q_BF16 && a->q_format != B200_MLA_Q_E4M3)
+        return fail(B200_MLA_ERR_INVALID_ARG, "bad q_format %d", a->q_format);
+    if (a->kv_format < B200_MLA_KV_E4M3 || a->kv_format > B200_MLA_KV_HYBRID)
+        return fail(B200_MLA_ERR_INVALID_ARG, "bad kv_format %d", a->kv_format);
+    if (!a->q || !a->kv_codes || !a->kv_indptr) return fail(B200_MLA_ERR_INVALID_ARG, "q, kv_codes and kv_indptr are required");
+    if (a->q_format == B200_MLA_Q_E4M3 && !a->q_scale) return fail(B200_MLA_ERR_INVALID_ARG, "q_scale is required for e4m3 Q");
+    if ((a->kv_format == B200_MLA_KV_E4M3 || a->kv_format == B200_MLA_KV_HYBRID) && !a->kv_scale)
+        return fail(B200_MLA_ERR_INVALID_ARG, "kv_scale is required for e4m3 / hybrid caches");
+    if (a->kv_format != B200_MLA_KV_E4M3 && !a->kv_block_scales)
+        return fail(B200_MLA_ERR_INVALID_ARG, "kv_block_scales is required for mxfp4 / hybrid caches");
+    if (a->kv_format == B200_MLA_KV_HYBRID && !a->kv_rope) return fail(B200_MLA_ERR_INVALID_ARG, "kv_rope is required for hybrid caches");
+    if (a->q_row_stride % 16 || a->q_head_stride % 16) return fail(B200_MLA_ERR_INVALID_ARG, "Q strides must be multiples of 16 elements");
+    if (a->kv_codes_stride % 16 || ((uintptr_t)a->kv_codes & 15)) return fail(B200_MLA_ERR_INVALID_ARG, "kv_codes must be 16-byte aligned with a stride multiple of 16");
+    if (a->kv_format == B200_MLA_KV_HYBRID && (a->kv_rope_stride % 16 || ((uintptr_t)a->kv_rope & 15)))
+        return fail(B200_MLA_ERR_INVALID_ARG, "kv_rope must be 16-byte aligned with a stride multiple of 16");
+    if ((uintptr_t)a->q & 15) return fail(B200_MLA_ERR_INVALID_ARG, "q must be 16-byte aligned");
+    if (a->page_size < 1) return fail(B200_MLA_ERR_INVALID_ARG, "page_size must be >= 1");
+    if (a->page_size > 1 && a->kv_indices && !a->kv_page_indptr)
+        return fail(B200_MLA_ERR_INVALID_ARG, "kv_page_indptr is required when page_size > 1");
+    if (!a->out && !a->out_o_f32) return fail(B200_MLA_ERR_INVALID_ARG, "one of out / out_o_f32 is required");
+    if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(B200_MLA_ERR_INVALID_ARG, "workspace must be non-NULL and 256-byte aligned");
+
+    MlaParams p;
+    memset(&p, 0, sizeof(p));
+    p.batch = a->batch; p.heads = a->heads; p.q_len = a->q_len; p.rows = a->heads * a->q_len;
+    p.q_format = a->q_format; p.kv_format = a->kv_format; p.causal = a->causal ? 1 : 0; p.page_size = a->page_size;
+    p.sm_scale = a->sm_scale;
+    p.q = a->q; p.q_row_stride = a->q_row_stride; p.q_head_stride = a->q_head_stride; p.q_scale = a->q_scale;
+    p.kv_codes = (const uint8_t*)a->kv_codes; p.kv_codes_stride = a->kv_codes_stride;
+    p.kv_bs = (const uint8_t*)a->kv_block_scales; p.kv_bs_stride = a->kv_block_scales_stride;
+    p.kv_rope = (const uint8_t*)a->kv_rope; p.kv_rope_stride = a->kv_rope_stride;
+    p.kv_scale = a->kv_scale; p.num_slots = a->num_slots;
+    p.kv_indptr = a->kv_indptr; p.kv_indices = a->kv_indices; p.kv_page_indptr = a->kv_page_indptr;
+    p.kv_pos_offset = a->kv_pos_offset; p.kv_total_len = a->kv_total_len;
+    p.out = (__nv_bfloat16*)a->out; p.out_o_f32 = a->out_o_f32; p.out_lse = a->out_lse;
+
+    const int sms = sm_count();
+    bool use_sm100 = false;
+    if (a->impl == B200_MLA_IMPL_TCGEN05) {
+        if (!sm100_supported(p)) return fail(B200_MLA_ERR_UNSUPPORTED, "the tcgen05 kernel does not cover this shape / format");
+        use_sm100 = true;
+    } else if (a->impl == B200_MLA_IMPL_AUTO) {
+        use_sm100 = sm100_supported(p);
+    } else if (a->impl != B200_MLA_IMPL_GENERIC) {
+        return fail(B200_MLA_ERR_INVALID_ARG, "bad impl %d", a->impl);
+    }
+
+    int ctas_per_sm;
+    if (use_sm100) { p.tile_tokens = 128; p.rows_per_cta = sm100_rows_per_cta(p); ctas_per_sm = 1; }
+    else { p.tile_tokens = 64; p.rows_per_cta = 16; ctas_per_sm = 2; }
+    const int groups = p.rows / p.rows_per_cta;
+    long long hint = a->total_kv_hint > 0 ? a->total_kv_hint : a->num_slots;
+    if (hint <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "total_kv_hint or num_slots must be positive");
+    const long long tiles_bound = (hint + p.tile_tokens - 1) / p.tile_tokens + a->batch;
+    long long G = (long long)ctas_per_sm * sms / groups;
+    if (G < 1) G = 1;
+    if (G > tiles_bound) G = tiles_bound;
+    p.num_ctas = (int)G;
+
+    const WsLayout L = ws_layout(a->batch, p.rows, kMaxCtasPerSm * sms);
+    if (a->workspace_bytes < L.total)
+        return fail(B200_MLA_ERR_WORKSPACE, "workspace of %lld bytes is smaller than the %lld required", (long long)a->workspace_bytes, L.total);
+    char* ws = (char*)a->workspace;
+    p.tile_prefix = (int*)(ws + L.prefix_off);
+    p.part_lse = (float*)(ws + L.lse_off);
+    p.part_o = (float*)(ws + L.o_off);
+
+    const bool prof = g_ev_start && g_ev_stop;
+    if (prof) cudaEventRecord(g_ev_start, stream);
+    cudaError_t e = use_sm100 ? launch_sm100(p, stream) : launch_generic(p, stream);
+    if (prof) cudaEventRecord(g_ev_stop, stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "stage-1 launch failed: %s", cudaGetErrorString(e));
+    e = launch_combine_spans(p, stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_set_stage1_events(void* start_event, void* stop_event) {
+    g_ev_start = (cudaEvent_t)start_event;
+    g_ev_stop = (cudaEvent_t)stop_event;
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_combine(const float* o_parts, const float* lse_parts, int32_t parts, int64_t rows, void* out,
+                         float* out_lse, void* stream) {
+    if (!o_parts || !lse_parts || !out) return fail(B200_MLA_ERR_INVALID_ARG, "o_parts, lse_parts and out are required");
+    if (parts <= 0 || rows <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "parts and rows must be positive");
+    if (rows > 0x7fffffffLL) return fail(B200_MLA_ERR_TOO_LARGE, "rows exceeds 2^31-1");
+    if (((uintptr_t)o_parts & 15) || ((uintptr_t)out & 7)) return fail(B200_MLA_ERR_INVALID_ARG, "o_parts must be 16-byte and out 8-byte aligned");
+    cudaError_t e = launch_combine_parts(o_parts, lse_parts, parts, rows, (__nv_bfloat16*)out, out_lse, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_quantize_fp8(const void* x_bf16, int64_t n, void* codes_out, float* scale_out, void* scratch,
+                              void* stream) {
+    if (!x_bf16 || !codes_out || !scale_out || !scratch) return fail(B200_MLA_ERR_INVALID_ARG, "NULL argument");
+    if (n <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "n must be positive");
+    if (((uintptr_t)x_bf16 & 15) || ((uintptr_t)codes_out & 7) || ((uintptr_t)scratch & 3))
+        return fail(B200_MLA_ERR_INVALID_ARG, "x must be 16-byte, codes 8-byte and scratch 4-byte aligned");
+    cudaError_t e = launch_quantize_fp8((const __nv_bfloat16*)x_bf16, n, (uint8_t*)codes_out, scale_out,
+                                        (unsigned int*)scratch, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "quantize launch failed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,138 @@
+// Shared device-side definitions for the MLA decode kernels: kernel parameter block, the
+// KV-span schedule that every stage-1 CTA and the combine kernel derive from kv_indptr, and the
+// byte-format decoders (e4m3fn, e2m1 + E8M0).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200mla {
+
+constexpr int QK_DIM = 576;
+constexpr int V_DIM = 512;
+constexpr int ROPE_DIM = 64;
+constexpr int MAX_BATCH = 8192;        // the per-CTA tile-prefix table lives in shared memory
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+enum { Q_BF16 = 0, Q_E4M3 = 1 };
+enum { KV_E4M3 = 0, KV_MXFP4 = 1, KV_HYBRID = 2 };
+
+struct MlaParams {
+    int batch, heads, q_len, rows;      // rows = q_len * heads (query rows per sequence)
+    int q_format, kv_format, causal, page_size;
+    float sm_scale;
+    int num_ctas;                       // G: stage-1 CTAs along x (KV spans)
+    int tile_tokens;                    // tokens per schedule tile (kernel specific)
+    int rows_per_cta;                   // query rows handled by one CTA (grid.y = rows / rows_per_cta)
+
+    const void* q; long long q_row_stride, q_head_stride; const float* q_scale;
+    const uint8_t* kv_codes; long long kv_codes_stride;
+    const uint8_t* kv_bs; long long kv_bs_stride;
+    const uint8_t* kv_rope; long long kv_rope_stride;
+    const float* kv_scale; long long num_slots;
+    const int* kv_indptr; const int* kv_indices; const int* kv_page_indptr;
+    const int* kv_pos_offset; const int* kv_total_len;
+
+    __nv_bfloat16* out; float* out_o_f32; float* out_lse;
+    float* part_o;                      // [G + batch - 1][rows][512] normalised partial O
+    float* part_lse;                    // [G + batch - 1][rows]      natural-log LSE
+    int* tile_prefix;                   // [batch + 1] exclusive prefix of tiles per sequence
+};
+
+// ---------------------------------------------------------------------------------------------
+// Schedule.  Sequence b owns tiles [P[b], P[b+1]) with ceil(len_b / tile_tokens) tiles; CTA w of
+// G owns the global tile range [w*TT/G, (w+1)*TT/G).  A (CTA, sequence) pair that does not cover
+// the whole sequence writes a partial into slot w + b, which is unique because both coordinates
+// are monotone along the chain of pairs.
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ int span_begin(int w, int total_tiles, int G) {
+    return (int)(((long long)w * total_tiles) / G);
+}
+// CTA whose span contains global tile t.
+__device__ __forceinline__ int cta_of_tile(int t, int total_tiles, int G) {
+    return (int)((((long long)(t + 1) * G + total_tiles - 1) / total_tiles) - 1);
+}
+
+// Fills prefix[0..batch] (shared memory) with the exclusive prefix of tiles per sequence.
+// All threads of the block must call it; ends with a __syncthreads().
+__device__ inline void build_tile_prefix(const int* __restrict__ kv_indptr, int batch, int tile_tokens,
+                                         int* prefix) {
+    for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+        int len = kv_indptr[b + 1] - kv_indptr[b];
+        prefix[b + 1] = len > 0 ? (len + tile_tokens - 1) / tile_tokens : 0;
+    }
+    if (threadIdx.x == 0) prefix[0] = 0;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        int carry = 0;
+        for (int base = 1; base <= batch; base += 32) {
+            int i = base + threadIdx.x;
+            int v = i <= batch ? prefix[i] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int n = __shfl_up_sync(0xffffffffu, v, o);
+                if ((int)threadIdx.x >= o) v += n;
+            }
+            v += carry;
+            if (i <= batch) prefix[i] = v;
+            carry = __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+}
+
+// First sequence b with prefix[b+1] > t (sequence containing global tile t).
+__device__ __forceinline__ int seq_of_tile(const int* prefix, int batch, int t) {
+    int lo = 0, hi = batch - 1;
+    while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (prefix[mid + 1] > t) hi = mid; else lo = mid + 1;
+    }
+    return lo;
+}
+
+// Cache slot of the token at position `pos` of sequence b.
+__device__ __forceinline__ long long slot_of(const MlaParams& p, int b, int seq_base, int page_base, int pos) {
+    if (p.kv_indices == nullptr) return (long long)seq_base + pos;
+    if (p.page_size == 1) return (long long)p.kv_indices[page_base + pos];
+    int pg = pos / p.page_size;
+    return (long long)p.kv_indices[page_base + pg] * p.page_size + (pos - pg * p.page_size);
+}
+
+// ---------------------------------------------------------------------------------------------
+// byte formats
+// ---------------------------------------------------------------------------------------------
+
+// two e4m3fn bytes (low 16 bits) -> two halves (exact)
+__device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
+    __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
+    return *reinterpret_cast<__half2*>(&r);
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+    __half_raw r = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&r));
+}
+
+// E8M0 byte -> float 2^(b-127).  Byte 0 gives 2^-127 (a denormal), 255 is NaN in the format.
+__device__ __forceinline__ float e8m0_to_float(uint8_t b) {
+    if (b == 255) return __int_as_float(0x7fc00000);
+    return b == 0 ? __int_as_float(0x00400000) : __int_as_float((int)b << 23);
+}
+
+// e2m1 code (4 bits, bit3 = sign) -> float
+__device__ __forceinline__ float e2m1_to_float(uint32_t c) {
+    // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6
+    uint32_t mag = c & 7u;
+    float v = mag < 2u ? 0.5f * (float)mag
+                       : __int_as_float((int)(((mag >> 1) + 126u) << 23) | (int)((mag & 1u) << 22));
+    return (c & 8u) ? -v : v;
+}
+
+}  // namespace b200mla

@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the MLA-decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1|c2|c3|c4]
+
+One step = one `custom_kernel(data)` call (Q quantisation where the workload has FP8 Q, split-KV
+stage 1, LSE combine) over one batch of seeded synthetic input with the shapes and value
+distributions of the BASELINE configuration (default c1: FP8 Q + FP8 KV, batch 32, 16 heads,
+KV length 4096, page size 1 behind a shuffled page table).
+
+Prints ONE JSON line (rank 0).  Keys beyond the base contract:
+  us_per_call, achieved_gbs   the other two forms of the headline metric
+  roofline                    the stage-1 kernel: algorithmic bytes per launch / its CUDA-event
+                              duration, against the measured HBM copy bandwidth
+  cpu_baseline                the CPU oracle (torch fp32 dequantise-then-attend) timed on this host
+  e2e                         the same call with every input staged from pinned host memory and
+                              the output copied back, copies inside the timed region
+
+With N > 1 (torchrun) every rank decodes its own batch (sequences are independent, no
+collective): weak scaling.  `--impl reference` times the CPU oracle port (the reference has no
+implementation that runs without AMD's aiter library) on rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (batch, q_len, heads, kv_len or (lo, hi), kv_format, q_format)
+    "c1": dict(batch=32, q_len=1, heads=16, kv_len=4096, kv_format="fp8", q_format="fp8",
+               desc="FP8 Q + FP8 KV, B32 H16 q1 S4096, page_size 1 shuffled (BASELINE configs[1])"),
+    "c2": dict(batch=64, q_len=1, heads=16, kv_len=8192, kv_format="mxfp4", q_format="bf16",
+               desc="bf16 Q + MXFP4 KV, B64 H16 q1 S8192, page_size 1 shuffled (BASELINE configs[2])"),
+    "c3": dict(batch=128, q_len=1, heads=128, kv_len=(1024, 16384), kv_format="hybrid", q_format="fp8",
+               desc="FP8 Q + hybrid KV, B128 H128 q1 S~U[1024,16384] (BASELINE configs[3])"),
+    "c4": dict(batch=8, q_len=2, heads=16, kv_len=131072, kv_format="mxfp4", q_format="bf16",
+               desc="bf16 Q + MXFP4 KV, B8 H16 q2 S131072 causal (BASELINE configs[4])"),
+}
+KV_ROW_BYTES = {"fp8": 576, "mxfp4": 306, "hybrid": 336}
+L2_BYTES = 126 << 20
+
+
+def algorithmic_bytes(w, total_kv):
+    q_elt = 1 if w["q_format"] == "fp8" else 2
+    rows = w["batch"] * w["q_len"] * w["heads"]
+    return (total_kv * KV_ROW_BYTES[w["kv_format"]] + rows * 576 * q_elt + rows * 512 * 2
+            + total_kv * 4 + (w["batch"] + 1) * 8)
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def make_lens(w, seed):
+    if isinstance(w["kv_len"], tuple):
+        g = torch.Generator().manual_seed(seed)
+        lo, hi = w["kv_len"]
+        return torch.randint(lo, hi + 1, (w["batch"],), generator=g).tolist()
+    return None
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 100 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.path = gpu_index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        try:
+            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
+            sm = [float(r[1]) for r in rows]
+            out["sm_mhz"] = statistics.median(sm)
+            out["sm_max_mhz"] = float(rows[0][2])
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            seen = set()
+            for r in rows:
+                for n, v in zip(names, r[5:9]):
+                    if v.strip().lower().startswith("active"):
+                        seen.add(n)
+            out["reasons"] = sorted(seen)
+            out["samples"] = len(rows)
+        except Exception:
+            pass
+        finally:
+            if self.path and os.path.exists(self.path):
+                os.unlink(self.path)
+        return out
+
+
+def cpu_oracle_step(host):
+    """One full workload call through the CPU oracle (torch fp32, all host threads)."""
+    from oracle import mla_oracle as mo
+    q, q_scale = host["q"], None
+    if host["w"]["q_format"] == "fp8":
+        q, q_scale = mo.quantize_fp8_per_tensor(q)
+    return mo.decode_from_data(q, q_scale, host["w"]["kv_format"], host["kv"], host["kv_indptr"].numpy(),
+                               host["kv_indices"].numpy(), host["sm_scale"], q_len=host["w"]["q_len"])
+
+
+def time_cpu(host, reps):
+    cpu_oracle_step(host)                                   # warm-up
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        cpu_oracle_step(host)
+        ts.append(time.perf_counter() - t0)
+    return statistics.median(ts)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
+    ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tcgen05"])
+    ap.add_argument("--cpu-reps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time eager API calls instead of a CUDA graph replay")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    n_gpus = max(args.gpus, world)
+    tokens_per_call = w["batch"] * w["q_len"]
+
+    import amd_optimization_challenge_b200.inputs as gen   # plain torch
+
+    def build_host(seed):
+        lens = make_lens(w, seed)
+        data = gen.generate_input(w["batch"], w["q_len"], w["kv_len"] if lens is None else max(lens), seed,
+                                  num_heads=w["heads"], kv_lens=lens, shuffle_pages=True,
+                                  formats=(w["kv_format"],), device="cpu")
+        q, kvd, qo, kvp, cfg = data
+        return dict(w=w, q=q, kv=kvd[w["kv_format"]], qo=qo, kv_indptr=kvp, kv_indices=cfg["kv_indices"],
+                    sm_scale=cfg["sm_scale"], cfg=cfg, total_kv=cfg["total_kv"])
+
+    # ------------------------------------------------------------------ reference arm (CPU)
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        host = build_host(1234)
+        torch.set_num_threads(os.cpu_count() or 1)
+        for _ in range(min(max(args.warmup, 1), 2)):
+            cpu_oracle_step(host)
+        steps = min(args.steps, 20)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            cpu_oracle_step(host)
+        dt = (time.perf_counter() - t0) / steps
+        val = tokens_per_call / dt
+        abytes = algorithmic_bytes(w, host["total_kv"])
+        line = {
+            "impl": "reference", "metric": "mla_decode_tokens_per_s", "value": val, "unit": "tokens/s",
+            "n_gpus": n_gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "us_per_call": dt * 1e6, "achieved_gbs": abytes / dt / 1e9,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['desc']}", "note": "CPU oracle port (torch fp32 "
+                       "dequantise-then-attend); the reference's own path needs AMD's aiter and cannot run here; "
+                       "each step is one full call, at most 20 steps are timed"},
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": f"{steps} full {args.workload} calls"},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line), flush=True)
+        return
+
+    # ------------------------------------------------------------------ our arm (GPU)
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import amd_optimization_challenge_b200 as pkg
+
+    host = build_host(1234 + rank)
+    abytes = algorithmic_bytes(w, host["total_kv"])
+    kv_bytes = sum(t.numel() * t.element_size() for t in host["kv"])
+    n_rot = max(2, -(-int(2.4 * L2_BYTES) // kv_bytes))         # rotate > 2.4x L2 worth of cache copies
+    n_rot = min(n_rot, 6)
+
+    def to_dev(h):
+        cfg = dict(h["cfg"])
+        cfg.update(kv_indices=h["kv_indices"].to(dev), kv_format=w["kv_format"], q_format=w["q_format"], impl=args.kernel)
+        return (h["q"].to(dev), {w["kv_format"]: tuple(t.to(dev) for t in h["kv"])}, h["qo"].to(dev),
+                h["kv_indptr"].to(dev), cfg)
+
+    base = to_dev(host)
+    rot = [base]
+    for _ in range(n_rot - 1):                                  # same bytes at distinct addresses
+        kv = tuple(t.clone() for t in base[1][w["kv_format"]])
+        rot.append((base[0], {w["kv_format"]: kv}, base[2], base[3], base[4]))
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- launch vehicle: a CUDA graph holding n_rot consecutive steps (one per cache copy), so
+    # that the timed region measures the GPU work and not the Python call overhead per step
+    for i in range(max(args.warmup, 3)):
+        out = pkg.custom_kernel(rot[i % n_rot])
+    barrier()
+    graph = None
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(n_rot):
+                    out = pkg.custom_kernel(rot[i])
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+
+    def run_steps(k):
+        if graph is None:
+            for i in range(k):
+                pkg.custom_kernel(rot[i % n_rot])
+            return
+        for _ in range(k // n_rot):
+            graph.replay()
+        for i in range(k % n_rot):
+            pkg.custom_kernel(rot[i])
+
+    # ---- clocks are sampled from before the pre-roll (same work, untimed) to after the timed region
+    sampler = ClockSampler(local_rank)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        t_end = time.perf_counter() + 0.7
+        while time.perf_counter() < t_end:
+            run_steps(8 * n_rot)
+            torch.cuda.synchronize()
+        barrier()
+        ev0.record()
+        run_steps(args.steps)                                   # exactly K steps
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        t_end = time.perf_counter() + 0.25
+        while time.perf_counter() < t_end:
+            run_steps(8 * n_rot)
+            torch.cuda.synchronize()
+    clocks = sampler.summary()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = n_gpus * tokens_per_call / (ms_per_step * 1e-3)
+
+    # ---- stage-1 kernel duration (CUDA events recorded by the library around that launch)
+    lib = pkg._cabi.lib
+    k_ms = []
+    pairs = []
+    nprof = min(args.steps, 50)
+    for i in range(nprof):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); b.record()                                  # instantiate the handles
+        pairs.append((a, b))
+    torch.cuda.synchronize()
+    for i, (a, b) in enumerate(pairs):
+        lib.b200_mla_set_stage1_events(ctypes.c_void_p(a.cuda_event), ctypes.c_void_p(b.cuda_event))
+        out = pkg.custom_kernel(rot[i % n_rot])
+    lib.b200_mla_set_stage1_events(None, None)
+    torch.cuda.synchronize()
+    k_ms = [a.elapsed_time(b) for a, b in pairs]
+    k_us = statistics.mean(k_ms) * 1e3
+    peak, peak_kind = measured_peak_gbs()
+    achieved = abytes / (k_us * 1e-6) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "kernel": "mla_decode stage 1", "kernel_us": k_us,
+                "algorithmic_bytes": abytes, "peak_source": f"of {peak_kind}"}
+
+    # ---- end to end: host buffers in, host buffer out, every step
+    pin = lambda t: t.contiguous().pin_memory()
+    h_q, h_kv = pin(host["q"]), tuple(pin(t) for t in host["kv"])
+    h_idx, h_ip, h_qo = pin(host["kv_indices"]), pin(host["kv_indptr"]), pin(host["qo"])
+    d_q, d_kv = torch.empty_like(base[0]), tuple(torch.empty_like(t) for t in base[1][w["kv_format"]])
+    d_idx, d_ip, d_qo = torch.empty_like(base[4]["kv_indices"]), torch.empty_like(base[3]), torch.empty_like(base[2])
+    h_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in (h_q, *h_kv, h_idx, h_ip, h_qo))
+    d2h = h_out.numel() * h_out.element_size()
+    cfg_e = dict(base[4]); cfg_e["kv_indices"] = d_idx
+
+    def e2e_step():
+        d_q.copy_(h_q, non_blocking=True)
+        for d, h in zip(d_kv, h_kv):
+            d.copy_(h, non_blocking=True)
+        d_idx.copy_(h_idx, non_blocking=True); d_ip.copy_(h_ip, non_blocking=True); d_qo.copy_(h_qo, non_blocking=True)
+        o = pkg.custom_kernel((d_q, {w["kv_format"]: d_kv}, d_qo, d_ip, cfg_e))
+        h_out.copy_(o, non_blocking=True)
+
+    e_steps = max(3, min(args.steps, 20))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    ev0.record()
+    for _ in range(e_steps):
+        e2e_step()
+    ev1.record()
+    barrier()
+    e_ms = ev0.elapsed_time(ev1) / e_steps
+    if world > 1:
+        t = torch.tensor([e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e_ms = float(t.item())
+    e2e = {"value": n_gpus * tokens_per_call / (e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+    # ---- CPU baseline (rank 0, single-GPU runs only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        t_cpu = time_cpu(host, args.cpu_reps)
+        cpu = {"value": tokens_per_call / t_cpu, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"median of {args.cpu_reps} full {args.workload} calls ({t_cpu * 1e3:.1f} ms each)",
+               "us_per_call": t_cpu * 1e6}
+
+    launches_per_step = 2 + (2 if w["q_format"] == "fp8" else 0)     # [amax, cast,] stage 1, combine
+    if rank == 0:
+        line = {
+            "metric": "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n_gpus,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "us_per_call": ms_per_step * 1e3, "achieved_gbs": abytes / (ms_per_step * 1e-3) / 1e9,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"fp8": "e4m3", "mxfp4": "mxfp4(e2m1+e8m0)", "hybrid": "mxfp4+e4m3"}[w["kv_format"]] + " x f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['desc']}", "kernel": args.kernel,
+                       "launch": "eager custom_kernel calls" if graph is None else f"CUDA graph of {n_rot} custom_kernel steps, replayed",
+                       "l2": f"rotating {n_rot} distinct copies of the {kv_bytes / 2**20:.1f} MiB cache (> 2x the 126 MB L2)",
+                       "per_gpu": "each rank decodes its own batch, no collective"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": launches_per_step * args.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,164 @@
+/*
+ * b200_mla.h - C ABI of the B200 (sm_100a) absorbed-MLA decode library (libb200mla.so).
+ *
+ * Plain pointers and sizes only; every pointer marked "device" must be valid on the CUDA device
+ * that is current when the call is made, `stream` is a cudaStream_t passed as void*.
+ * All entry points return 0 on success or a negative b200_mla_status; none of them synchronises
+ * the stream or reads device memory on the host.
+ *
+ * Each entry point names the reference interface it replaces (paths relative to the reference
+ * project root).
+ */
+#ifndef B200_MLA_H
+#define B200_MLA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_MLA_QK_DIM 576   /* 512 latent + 64 rope (reference.py:40-46) */
+#define B200_MLA_V_DIM 512    /* V = first 512 dims of the same cache row (task.py:20-23) */
+#define B200_MLA_ROPE_DIM 64
+
+typedef enum {
+    B200_MLA_OK = 0,
+    B200_MLA_ERR_INVALID_ARG = -1,      /* null pointer, bad stride / alignment, bad enum */
+    B200_MLA_ERR_UNSUPPORTED = -2,      /* combination the kernels do not implement */
+    B200_MLA_ERR_WORKSPACE = -3,        /* workspace too small */
+    B200_MLA_ERR_CUDA = -4,             /* a CUDA runtime call failed; see b200_mla_last_error */
+    B200_MLA_ERR_TOO_LARGE = -5         /* size beyond a documented limit */
+} b200_mla_status;
+
+typedef enum { B200_MLA_Q_BF16 = 0, B200_MLA_Q_E4M3 = 1 } b200_mla_q_format;
+
+typedef enum {
+    B200_MLA_KV_E4M3 = 0,    /* [slots, 576] e4m3fn codes + fp32 per-tensor scale            */
+    B200_MLA_KV_MXFP4 = 1,   /* [slots, 288] e2m1 x2 (even element in the low nibble)        */
+                             /* + [slots, >=18] E8M0, one per 32 elements                    */
+    B200_MLA_KV_HYBRID = 2   /* latent: [slots, 256] e2m1 x2 + [slots, 16] E8M0;             */
+                             /* rope: [slots, 64] e4m3fn + fp32 per-tensor scale             */
+} b200_mla_kv_format;
+
+typedef enum {
+    B200_MLA_IMPL_AUTO = 0,      /* tcgen05 kernel where it applies, else the generic one */
+    B200_MLA_IMPL_GENERIC = 1,   /* warp-level tensor-core kernel, every shape */
+    B200_MLA_IMPL_TCGEN05 = 2    /* tcgen05 / TMEM kernel; B200_MLA_ERR_UNSUPPORTED if it does not apply */
+} b200_mla_impl;
+
+/*
+ * Arguments of one decode call.  The layout mirrors what the reference's native entry points
+ * receive: aiter.mla_decode_stage1_asm_fwd(q, kv4d, qo_indptr, kv_indptr, kv_indices,
+ * kv_last_page_lens, ..., sm_scale, logits, attn_lse, o, final_lse, q_scale, kv_scale)
+ * (mixed-mla/versions/v34_direct_asm/submission.py:455-476) and the HIP extension
+ * mla_mxfp4_v5_forward(Q_fp8, K_fp4, K_scale, V_fp8, kv_indptr, sm_scale, kv_scale, B, splits)
+ * (mixed-mla/versions/hip_mxfp4_v5/submission.py:720-730).
+ */
+typedef struct {
+    /* ---- problem ---- */
+    int32_t batch;            /* sequences */
+    int32_t heads;            /* query heads sharing the single latent KV head; multiple of 16 */
+    int32_t q_len;            /* queries per sequence (1, or 2..4 for speculative decode) */
+    int32_t q_format;         /* b200_mla_q_format */
+    int32_t kv_format;        /* b200_mla_kv_format */
+    int32_t causal;           /* non-zero: query j sees key position p iff p <= total_len - q_len + j */
+    int32_t page_size;        /* tokens per page; kv_indices holds page ids. 1 for the reference layout */
+    int32_t impl;             /* b200_mla_impl */
+    float sm_scale;           /* softmax scale (reference: 1/sqrt(576), reference.py:46) */
+    int32_t reserved0;
+
+    /* ---- Q: [batch*q_len, heads, 576] ---- */
+    const void *q;            /* device; bf16 or e4m3fn */
+    int64_t q_row_stride;     /* elements between consecutive query rows (heads*576 when dense) */
+    int64_t q_head_stride;    /* elements between heads (576 when dense) */
+    const float *q_scale;     /* device fp32[1]; required for B200_MLA_Q_E4M3, else NULL */
+
+    /* ---- KV cache planes (device) ---- */
+    const void *kv_codes;     /* e4m3: [slots,576]; mxfp4: [slots,288]; hybrid: latent [slots,256] */
+    int64_t kv_codes_stride;  /* bytes between slots; multiple of 16 */
+    const void *kv_block_scales;   /* E8M0 bytes (mxfp4: >=18 per slot, hybrid: >=16); NULL for e4m3 */
+    int64_t kv_block_scales_stride;/* bytes between slots (the reference pads this plane, reference.py:125-148) */
+    const void *kv_rope;      /* hybrid only: [slots,64] e4m3fn */
+    int64_t kv_rope_stride;   /* bytes between slots; multiple of 16 */
+    const float *kv_scale;    /* device fp32[1]: per-tensor scale of the e4m3 codes (e4m3: whole row, hybrid: rope) */
+    int64_t num_slots;        /* rows in the cache planes (bounds for kv_indices) */
+
+    /* ---- page table ---- */
+    const int32_t *kv_indptr;     /* device int32[batch+1], token offsets (task.py:14) */
+    const int32_t *kv_indices;    /* device int32[...] page ids, or NULL: token t of the batch lives in slot t,
+                                     exactly the arange the reference builds (reference.py:245) */
+    const int32_t *kv_page_indptr;/* device int32[batch+1] offsets into kv_indices; NULL when page_size == 1
+                                     (then kv_indptr is used) */
+    int64_t total_kv_hint;        /* upper bound on kv_indptr[batch] known to the host (sizes the grid) */
+
+    /* ---- sharded sequences (cross-GPU split-KV); NULL when the call sees whole sequences ---- */
+    const int32_t *kv_pos_offset; /* device int32[batch]: position of the shard's first key in the sequence */
+    const int32_t *kv_total_len;  /* device int32[batch]: full sequence length (for the causal mask) */
+
+    /* ---- outputs (device) ---- */
+    void *out;                /* bf16 [batch*q_len, heads, 512], dense; may be NULL if out_o_f32 is set */
+    float *out_o_f32;         /* optional: normalised fp32 O [batch*q_len, heads, 512] (partial of a shard) */
+    float *out_lse;           /* optional: fp32 natural-log LSE [batch*q_len, heads]; -inf for an empty key set */
+
+    /* ---- scratch ---- */
+    void *workspace;          /* device, 256-byte aligned */
+    int64_t workspace_bytes;  /* >= b200_mla_workspace_bytes() */
+} b200_mla_decode_args;
+
+/* Library / ABI version (major*1000 + minor). */
+int32_t b200_mla_version(void);
+
+/* Human-readable text for the last failing call on the calling thread. */
+const char *b200_mla_last_error(void);
+
+/*
+ * Scratch size for one decode call on the current device.
+ * Replaces aiter.get_mla_metadata_info_v1 (reference.py:174-182), which sizes the reference's six
+ * work buffers, and the partial-buffer allocation of _get_mxfp4_buffers (mixed-mla/submission.py:301-318).
+ */
+int64_t b200_mla_workspace_bytes(int32_t batch, int32_t heads, int32_t q_len);
+
+/*
+ * Split-KV decode: stage 1 (partial attention per KV span) followed by the log-sum-exp combine,
+ * both enqueued on `stream`.
+ * Replaces mla_decode_fwd / mla_decode_stage1_asm_fwd + mla_reduce_v1
+ * (mixed-mla/asm_dumps/aiter_mla.py:149-470), the Triton pair _mla_mxfp4_stage1 / _mla_mxfp4_reduce
+ * (mixed-mla/submission.py:122-294) and the work-list builder get_mla_metadata_v1
+ * (reference.py:184-200): the KV spans are derived on the device from kv_indptr.
+ */
+int32_t b200_mla_decode(const b200_mla_decode_args *args, void *stream);
+
+/*
+ * Log-sum-exp merge of `parts` normalised partial results, e.g. the per-GPU shards of a
+ * split-KV sequence after an all-gather:
+ *   o_parts  device fp32 [parts, rows, 512], lse_parts device fp32 [parts, rows]
+ *   out      device bf16 [rows, 512];  out_lse optional device fp32 [rows]
+ * Replaces _mla_mxfp4_reduce (mixed-mla/submission.py:257-294), aiter.mla_reduce_v1
+ * (mixed-mla/asm_dumps/aiter_mla.py:421-430) and the (O, LSE) form of
+ * competitor_submissions/dgavriloff_v114_hybrid_mxfp4k_fp8v.py:131-160.
+ */
+int32_t b200_mla_combine(const float *o_parts, const float *lse_parts, int32_t parts, int64_t rows,
+                         void *out, float *out_lse, void *stream);
+
+/*
+ * Dynamic per-tensor e4m3fn quantisation of a dense bf16 tensor of n elements with the arithmetic
+ * order of the reference's quantize_fp8 (reference.py:65-80; fused Triton form
+ * mixed-mla/fused_fp8_quant.py:93-148): amax, scale = amax/448 and x/scale rounded to bf16, clamp,
+ * cast.  `scale_out` (device fp32[1]) receives the scale; `scratch` is device, >= 4 bytes.
+ */
+int32_t b200_mla_quantize_fp8(const void *x_bf16, int64_t n, void *codes_out, float *scale_out,
+                              void *scratch, void *stream);
+
+/*
+ * Profiling aid (no counterpart in the reference, whose harness times whole calls, eval.py:225-261):
+ * while both events (cudaEvent_t) are non-NULL, every b200_mla_decode issued by the calling thread
+ * records `start` before and `stop` after its stage-1 kernel on the call's stream.  Pass NULLs to
+ * switch it off.
+ */
+int32_t b200_mla_set_stage1_events(void *start_event, void *stop_event);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_MLA_H */
