@@ -36,11 +36,14 @@ __global__ void __launch_bounds__(128) combine_spans_kernel(const MlaParams p) {
     const int w0 = cta_of_tile(t0, TT, G), w1 = cta_of_tile(t1 - 1, TT, G);
     if (w0 == w1) return;                                 // finished by a single stage-1 CTA
     float M = -INFINITY;
-    for (int w = w0; w <= w1; ++w) M = fmaxf(M, p.part_lse[(long long)(w + b) * p.rows + r]);
+    // CTAs whose span is empty (G > total tiles) wrote nothing: skip them
+    for (int w = w0; w <= w1; ++w)
+        if (span_begin(w, TT, G) < span_begin(w + 1, TT, G)) M = fmaxf(M, p.part_lse[(long long)(w + b) * p.rows + r]);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float den = 0.f;
     if (M > -INFINITY) {
         for (int w = w0; w <= w1; ++w) {
+            if (span_begin(w, TT, G) >= span_begin(w + 1, TT, G)) continue;
             const long long slot = w + b;
             const float wt = expf(p.part_lse[slot * p.rows + r] - M);
             const float4 v = *reinterpret_cast<const float4*>(p.part_o + (slot * p.rows + r) * V_DIM + d);
