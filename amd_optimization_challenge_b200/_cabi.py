@@ -22,7 +22,7 @@ class DecodeArgs(ctypes.Structure):
     """struct b200_mla_decode_args"""
     _fields_ = [
         ("batch", _i32), ("heads", _i32), ("q_len", _i32), ("q_format", _i32), ("kv_format", _i32),
-        ("causal", _i32), ("page_size", _i32), ("impl", _i32), ("sm_scale", _f32), ("reserved0", _i32),
+        ("causal", _i32), ("page_size", _i32), ("impl", _i32), ("sm_scale", _f32), ("max_ctas", _i32),
         ("q", _vp), ("q_row_stride", _i64), ("q_head_stride", _i64), ("q_scale", _vp),
         ("kv_codes", _vp), ("kv_codes_stride", _i64),
         ("kv_block_scales", _vp), ("kv_block_scales_stride", _i64),

@@ -10,7 +10,7 @@
 namespace b200mla {
 cudaError_t launch_generic(const MlaParams& p, cudaStream_t stream);
 size_t generic_smem_bytes(int batch);
-cudaError_t launch_sm100(const MlaParams& p, cudaStream_t stream);
+cudaError_t launch_sm100(const MlaParams& p, int* status, cudaStream_t stream);
 bool sm100_supported(const MlaParams& p);
 int sm100_rows_per_cta(const MlaParams& p);
 cudaError_t launch_combine_spans(const MlaParams& p, cudaStream_t stream);
@@ -51,13 +51,15 @@ int sm_count() {
 constexpr int kMaxCtasPerSm = 2;
 inline long long align256(long long x) { return (x + 255) & ~255LL; }
 
-struct WsLayout { long long prefix_off, lse_off, o_off, total; };
+// workspace: [status word | tile prefix | partial LSE | partial O]
+struct WsLayout { long long status_off, prefix_off, lse_off, o_off, total; };
 
 WsLayout ws_layout(int batch, int rows, int g_max) {
     WsLayout L;
     const long long slots = (long long)g_max + batch;
-    L.prefix_off = 0;
-    L.lse_off = align256((long long)(batch + 1) * 4);
+    L.status_off = 0;
+    L.prefix_off = 256;
+    L.lse_off = L.prefix_off + align256((long long)(batch + 1) * 4);
     L.o_off = L.lse_off + align256(slots * rows * 4);
     L.total = L.o_off + align256(slots * rows * (long long)V_DIM * 4);
     return L;
@@ -141,6 +143,7 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     long long G = (long long)ctas_per_sm * sms / groups;
     if (G < 1) G = 1;
     if (G > tiles_bound) G = tiles_bound;
+    if (a->max_ctas > 0 && G > a->max_ctas) G = a->max_ctas;
     p.num_ctas = (int)G;
 
     const WsLayout L = ws_layout(a->batch, p.rows, kMaxCtasPerSm * sms);
@@ -153,7 +156,7 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
 
     const bool prof = g_ev_start && g_ev_stop;
     if (prof) cudaEventRecord(g_ev_start, stream);
-    cudaError_t e = use_sm100 ? launch_sm100(p, stream) : launch_generic(p, stream);
+    cudaError_t e = use_sm100 ? launch_sm100(p, (int*)(ws + L.status_off), stream) : launch_generic(p, stream);
     if (prof) cudaEventRecord(g_ev_stop, stream);
     if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "stage-1 launch failed: %s", cudaGetErrorString(e));
     e = launch_combine_spans(p, stream);

@@ -1,10 +1,638 @@
-// tcgen05 / TMEM stage-1 kernel (placeholder until the kernel lands: reports "not applicable").
+// Stage-1 MLA decode on the 5th-generation tensor cores (tcgen05) with TMEM accumulators.
+//
+// Swap-AB formulation, so that the 128-row MMA dimension is filled by KV tokens and the small
+// dimension (16..32 query rows) is the MMA N:
+//     S^T[128 tok x N]   = K[128 tok x 576] . Q^T          A = K tile (K-major, 128B swizzle), B = Q
+//     O^T[512 x 2N]     += V^T[512 x 128 tok] . P^T         A = the same tile read MN-major (V = first
+//                                                           512 dims of K), B = P written by the
+//                                                           softmax warps, 4 M-blocks of 128 dims
+// Both contractions run as kind::f8f6f4 on e4m3 operands with fp32 accumulation in TMEM.  P is
+// split into two e4m3 terms (P = hi + lo/16, the two halves of the 2N columns) so that the
+// probabilities keep ~8 significant bits.
+//
+// Roles (192 threads):  warps 0-3  softmax / correction / epilogue (one TMEM lane per thread)
+//                       warp  4    tcgen05.mma issue (one lane), TMEM allocation
+//                       warp  5    paged gather by TMA: cp.async.bulk.tensor ... tile::gather4 fetches
+//                                  four cache rows named by the page table per instruction (4 x 128 B)
+//                                  straight into the 128B-swizzled UMMA layout; 160 instructions per
+//                                  128-token tile, completion counted in bytes on an mbarrier.
+//                                  (16-byte cp.async through the LSU topped out near 22 B/clk/SM.)
+// Synchronisation is mbarrier based; every wait is bounded and on expiry sets a status word.
+// Online softmax runs in the exp2 domain with lazy re-centering: the reference maximum is only
+// raised (and O rescaled in TMEM) when a score exceeds it by more than 2^4.
+//
+// Role in the reference: the split-KV stage-1 kernels (mixed-mla/submission.py:122-250,
+// mixed-mla/versions/hip_mxfp4_v5/submission.py:214-656).
+#include <cuda.h>
+
 #include "mla_common.cuh"
 
 namespace b200mla {
+namespace sm100 {
 
-bool sm100_supported(const MlaParams&) { return false; }
-int sm100_rows_per_cta(const MlaParams&) { return 16; }
-cudaError_t launch_sm100(const MlaParams&, cudaStream_t) { return cudaErrorNotSupported; }
+constexpr int TILE = 128;                 // tokens per tile = UMMA M
+constexpr int NS = 2;                     // cache tile stages
+constexpr int PANEL_BYTES = TILE * 128;   // one 128-byte-wide swizzled panel of a tile
+constexpr int NPANEL = 5;                 // 576 B per row = 4.5 panels (the last one half used)
+constexpr int STAGE_BYTES = NPANEL * PANEL_BYTES;
+constexpr int THREADS = 192;
+constexpr float RECENTER = 4.0f;          // log2 units
+constexpr float P_SCALE_LOG2 = 4.0f;      // probabilities are stored multiplied by 2^4
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // ~1 s: far beyond any legitimate wait of this kernel
+
+enum { ST_OK = 0, ST_TIMEOUT = 1 };
+
+// Optional timeline instrumentation (compiled in only with -DB200MLA_TRACE; development aid).
+#ifdef B200MLA_TRACE
+__device__ long long* g_trace = nullptr;
+#define TRACE(id, tile) do { if (g_trace && blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_trace[(tile) * 16 + (id)] = clock64(); } while (0)
+#else
+#define TRACE(id, tile) do { } while (0)
+#endif
+
+// ----------------------------------------------------------------------------------------------
+// PTX wrappers
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(20000u) : "memory");   // may sleep up to 20 us per try
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_nb(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Wait for completion number `n` (0-based) of the barrier; n = -1 passes at once.
+// The wait is bounded: when it expires the thread raises the CTA's abort flag and carries on, and
+// every later wait of the CTA returns at once.  Control flow never depends on the outcome, so all
+// threads still meet at the same barriers; the results of such a launch are garbage and the
+// kernel reports ST_TIMEOUT through the status word.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, int n, volatile int* abort_flag) {
+    const uint32_t parity = (uint32_t)n & 1u;
+    if (mbar_try(bar, parity)) return;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try(bar, parity)) return;
+        if ((it & 63u) == 0u) {
+            if (*abort_flag) return;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
+        }
+    }
+    *abort_flag = 1;
+}
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Four rows (r0..r3) of a 2-D tensor, `box` bytes each starting at byte column x, land in four
+// consecutive 128-byte rows of shared memory with the tensor map's swizzle applied.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int r0, int r1, int r2, int r3) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+// The barrier receives one arrival once all cp.async copies issued so far by this thread have landed.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+__device__ __forceinline__ void named_bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+__device__ __forceinline__ bool named_bar_or(int id, int n, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"(id), "r"(n), "r"((uint32_t)pred) : "memory");
+    return r != 0;
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(addr) : "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets (all
+// in 16-byte units), descriptor version 1, swizzle mode in the top bits.
+constexpr uint64_t SWIZZLE_NONE = 0, SWIZZLE_128B = 2;
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint64_t swizzle) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (swizzle << 61);
+}
+// Same layout, start address moved by `bytes` (the address field never carries: smem < 256 KB).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
+// Instruction descriptor, kind::f8f6f4: fp32 accumulate, e4m3 x e4m3, M = 128.
+__host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// pack four floats into four e4m3 bytes (round to nearest even, saturating)
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
+    return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+__device__ __forceinline__ float2 unpack_e4m3x2(uint16_t v) { return __half22float2(e4m3x2_to_half2(v)); }
+
+// ----------------------------------------------------------------------------------------------
+template <int N>
+struct Layout {
+    static constexpr int Q_BYTES = NPANEL * N * 128;
+    static constexpr int P_CHUNKS = 2 * N / 16;                  // 16-column chunks of [hi | lo]
+    static constexpr int P_BUF_BYTES = P_CHUNKS * TILE * 16;
+    static constexpr int OFF_Q = NS * STAGE_BYTES;
+    static constexpr int OFF_P = OFF_Q + Q_BYTES;
+    static constexpr int OFF_MISC = OFF_P + 2 * P_BUF_BYTES;
+    static constexpr int TMEM_S = 0;                              // two S buffers of N columns
+    static constexpr int TMEM_O = 2 * N;                          // four O blocks of 2N columns
+    static constexpr int TMEM_COLS = (10 * N <= 256) ? 256 : 512;
+};
+
+struct Misc {
+    uint64_t kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], p_empty[2], q_full;
+    uint32_t tmem_base;
+    int abort_flag;
+    float red[4][32];            // cross-warp exchange (max / sum), 32 = max N
+};
+
+template <int N>
+__global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaParams p, int* status,
+                                                                      const __grid_constant__ CUtensorMap kv_map) {
+    using L = Layout<N>;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    Misc& ms = *reinterpret_cast<Misc*>(smem + L::OFF_MISC);
+    int* prefix = reinterpret_cast<int*>(smem + L::OFF_MISC + sizeof(Misc));
+    const uint32_t smem_base = smem_u32(smem);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int w = blockIdx.x, G = p.num_ctas;
+    const int row0 = blockIdx.y * N;
+    if (tid == 0) TRACE(0, 63);
+
+    if (tid == 0) {
+        for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], 1); mbar_init(&ms.kv_empty[i], 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128);
+            mbar_init(&ms.p_full[i], 128); mbar_init(&ms.p_empty[i], 1);
+        }
+        mbar_init(&ms.q_full, 128);
+        ms.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) { tmem_alloc(&ms.tmem_base, L::TMEM_COLS); tmem_relinquish(); }
+    build_tile_prefix(p.kv_indptr, p.batch, TILE, prefix);       // ends with __syncthreads()
+    tc_fence_after();
+    const uint32_t tmem = ms.tmem_base;
+    if (tid == 0) TRACE(1, 63);
+    const int TT = prefix[p.batch];
+    if (w == 0 && blockIdx.y == 0)
+        for (int i = tid; i <= p.batch; i += THREADS) p.tile_prefix[i] = prefix[i];
+
+    const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
+
+    const float q_sc = __ldg(p.q_scale), kv_sc = __ldg(p.kv_scale);
+    const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
+    const float out_scale = kv_sc;
+    volatile int* abort_flag = &ms.abort_flag;
+
+    int g0 = 0;                       // tiles processed so far by this CTA (drives stages and phases)
+    int pair_idx = 0;                 // (CTA, sequence) pairs processed so far
+    int b = t_begin < t_end ? seq_of_tile(prefix, p.batch, t_begin) : 0;
+    int t = t_begin;
+    while (t < t_end) {
+        if (*abort_flag) break;       // uniform: read right after a __syncthreads()
+        while (prefix[b + 1] <= t) ++b;
+        const int seq_t0 = prefix[b], seq_t1 = prefix[b + 1];
+        const int my_t1 = min(t_end, seq_t1);
+        const int n_tiles = my_t1 - t;
+        const int seq_base = p.kv_indptr[b];
+        const int seq_len = p.kv_indptr[b + 1] - seq_base;
+        const int page_base = p.kv_page_indptr ? p.kv_page_indptr[b] : seq_base;
+        const int pos_off = p.kv_pos_offset ? p.kv_pos_offset[b] : 0;
+        const int tot_len = p.kv_total_len ? p.kv_total_len[b] : seq_len;
+        const int pos_first = (t - seq_t0) * TILE;
+
+        if (warp == 5) {
+            // =========================== paged gather by TMA (one warp) ===========================
+            // lane l owns tokens 4l..4l+3 of every tile: one gather4 per 128-byte panel of the row
+            auto slots_for = [&](int i, int (&sl)[4]) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int pos = pos_first + i * TILE + 4 * lane + u;
+                    // rows past the end of the sequence are fetched from an out-of-range row: zero fill
+                    sl[u] = pos < seq_len ? (int)slot_of(p, b, seq_base, page_base, pos) : (int)p.num_slots;
+                }
+            };
+            int sl[4];
+            slots_for(0, sl);
+            for (int i = 0; i < n_tiles; ++i) {
+                const int g = g0 + i, st = g % NS;
+                mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
+                if (lane == 0) { TRACE(0, g); mbar_arrive_expect_tx(&ms.kv_full[st], STAGE_BYTES); }
+                __syncwarp();
+                const uint32_t dst = smem_base + st * STAGE_BYTES + lane * 512;
+#pragma unroll
+                for (int j = 0; j < NPANEL; ++j)
+                    tma_gather4(dst + j * PANEL_BYTES, &kv_map, &ms.kv_full[st], j * 128, sl[0], sl[1], sl[2], sl[3]);
+                if (lane == 0) TRACE(1, g);
+                if (i + 1 < n_tiles) slots_for(i + 1, sl);
+            }
+        } else if (warp == 4) {
+            // =========================== MMA issue (one lane) ===========================
+            if (lane == 0) {
+                constexpr uint32_t IDESC_QK = make_idesc(N, false, false);
+                constexpr uint32_t IDESC_PV = make_idesc(2 * N, true, true);
+                // descriptor bases; per-MMA descriptors differ only in the start address
+                const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                  // + stage
+                const uint64_t d_qk_b = make_desc(smem_base + L::OFF_Q, 16, 1024, SWIZZLE_128B);
+                const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
+                const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, TILE * 16, SWIZZLE_NONE); // + buffer
+                auto issue_pv = [&](int g, bool first) {
+                    const int st = g % NS, pb = g & 1;
+                    TRACE(4, g);
+                    tc_fence_after();
+                    const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
+                    const uint64_t b0 = desc_advance(d_pv_b, pb * L::P_BUF_BYTES);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            umma_f8(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
+                                    desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
+                        }
+                    }
+                    umma_commit(&ms.kv_empty[st]);
+                    umma_commit(&ms.p_empty[pb]);
+                    TRACE(5, g);
+                };
+                auto issue_qk = [&](int g) {
+                    const int st = g % NS, sb = g & 1;
+                    TRACE(2, g);
+                    tc_fence_after();
+                    const uint64_t a0 = desc_advance(d_qk_a, st * STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 18; ++k) {
+                        umma_f8(tmem + L::TMEM_S + sb * N, desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32),
+                                desc_advance(d_qk_b, (k >> 2) * (N * 128) + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&ms.s_full[sb]);
+                    TRACE(3, g);
+                };
+                // Event driven: PV(g) as soon as P(g) is published (it frees the tile for the next gather),
+                // else QK of the next tile as soon as that tile has landed and its S buffer is free.
+                mbar_wait(&ms.q_full, pair_idx, abort_flag);   // Q of this sequence is in shared memory
+                int nq = 0, nv = 0;
+                long long t_idle = clock64();
+                uint32_t spins = 0;
+                while (nv < n_tiles) {
+                    const int gv = g0 + nv, gq = g0 + nq;
+                    if (nv < nq && mbar_try_nb(&ms.p_full[gv & 1], (uint32_t)(gv / 2) & 1u)) {
+                        issue_pv(gv, nv == 0);
+                        ++nv; spins = 0;
+                    } else if (nq < n_tiles && mbar_try_nb(&ms.kv_full[gq % NS], (uint32_t)(gq / NS) & 1u) &&
+                               mbar_try_nb(&ms.s_empty[gq & 1], (uint32_t)(gq / 2 - 1) & 1u)) {
+                        issue_qk(gq);
+                        ++nq; spins = 0;
+                    } else if ((++spins & 63u) == 0u) {
+                        if (spins == 64u) t_idle = clock64();
+                        if (*abort_flag || clock64() - t_idle > WAIT_LIMIT_CYCLES) {
+                            *abort_flag = 1;                    // give up waiting; issue the rest regardless so that every commit still arrives
+                            if (nq < n_tiles) { issue_qk(gq); ++nq; } else { issue_pv(gv, nv == 0); ++nv; }
+                        }
+                    }
+                }
+            }
+        } else {
+            // =========================== softmax / correction / epilogue (128 threads) ===========
+            const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+            // ---- Q rows of this sequence -> swizzled K-major panels, published to the MMA warp
+            // (the previous pair's MMAs have all completed: its epilogue waited for the last PV)
+            for (int i = tid; i < N * 36; i += 128) {
+                const int r = i / 36, c = i - r * 36;
+                const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
+                                     (long long)(b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+                *reinterpret_cast<uint4*>(smem + L::OFF_Q + (c >> 3) * (N * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+            }
+            fence_proxy_async();
+            mbar_arrive(&ms.q_full);
+            if (tid == 0) TRACE(2, 63);
+            // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key
+            float nm[N], l_acc[N];
+#pragma unroll
+            for (int c = 0; c < N; ++c) { nm[c] = INFINITY; l_acc[c] = 0.0f; }
+            // token position pos is visible to the rows of 16-column chunk q iff pos < lim[q]
+            // (heads is a multiple of 16, so the query index j is constant inside a chunk)
+            int lim[N / 16], lim_min = 0x7fffffff;
+#pragma unroll
+            for (int q = 0; q < N / 16; ++q) {
+                const int j = (row0 + 16 * q) / p.heads;
+                const int causal_lim = p.causal ? (tot_len - p.q_len + j + 1 - pos_off) : 0x7fffffff;
+                lim[q] = min(seq_len, causal_lim);
+                lim_min = min(lim_min, lim[q]);
+            }
+            // per-column reduction over the 128 threads; result replicated in every thread
+            auto reduce_cols = [&](float (&v)[N], bool is_max) {
+#pragma unroll
+                for (int c = 0; c < N; ++c) {
+                    float x = v[c];
+#pragma unroll
+                    for (int o = 16; o >= 1; o >>= 1) {
+                        const float y = __shfl_xor_sync(0xffffffffu, x, o);
+                        x = is_max ? fmaxf(x, y) : x + y;
+                    }
+                    if (lane == 0) ms.red[warp][c] = x;
+                }
+                named_bar_sync(1, 128);
+#pragma unroll
+                for (int c = 0; c < N; ++c) {
+                    const float a0 = ms.red[0][c], a1 = ms.red[1][c], a2 = ms.red[2][c], a3 = ms.red[3][c];
+                    v[c] = is_max ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : (a0 + a1) + (a2 + a3);
+                }
+                named_bar_sync(1, 128);
+            };
+            for (int i = 0; i < n_tiles; ++i) {
+                const int g = g0 + i, sb = g & 1;
+                mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
+                if (tid == 0) TRACE(6, g);
+                tc_fence_after();
+                float s[N];
+#pragma unroll
+                for (int c0 = 0; c0 < N; c0 += 16) tmem_ld16(tmem + lane_base + L::TMEM_S + sb * N + c0, s + c0);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(&ms.s_empty[sb]);
+
+                // x = log2-domain exponent of the stored probability: score*scale - m_ref + P_SCALE_LOG2
+                const int pos = pos_first + i * TILE + tid;
+                const bool masked_tile = pos_first + (i + 1) * TILE > lim_min;       // uniform
+                float x[N];
+#pragma unroll
+                for (int c = 0; c < N; ++c) x[c] = fmaf(s[c], score_scale, nm[c]);
+                if (masked_tile) {
+#pragma unroll
+                    for (int c = 0; c < N; ++c) if (pos >= lim[c / 16]) x[c] = -INFINITY;
+                }
+                float xm = x[0];
+#pragma unroll
+                for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
+                if (tid == 0) TRACE(7, g);
+                const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
+                if (tid == 0) TRACE(8, g);
+                if (recenter) {
+                    float mx[N];
+#pragma unroll
+                    for (int c = 0; c < N; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : s[c] * score_scale;
+                    reduce_cols(mx, true);
+                    float f[N];
+                    bool any = false;
+#pragma unroll
+                    for (int c = 0; c < N; ++c) {
+                        const float m_old = P_SCALE_LOG2 - nm[c];                     // -inf for a fresh column
+                        const float m_new = fmaxf(m_old, mx[c]);
+                        f[c] = (m_new == m_old) ? 1.0f : (m_old == -INFINITY ? 0.0f : ex2(m_old - m_new));
+                        any |= f[c] != 1.0f;
+                        nm[c] = P_SCALE_LOG2 - m_new;
+                        l_acc[c] *= f[c];
+                        x[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : fmaf(s[c], score_scale, nm[c]);
+                    }
+                    if (i > 0 && any) {
+                        // O holds tiles 0..i-1 once PV(g-1) has completed; nothing else touches it until P(g) is published
+                        mbar_wait(&ms.p_empty[(g - 1) & 1], (g - 1) / 2, abort_flag);
+                        tc_fence_after();
+#pragma unroll
+                        for (int jb = 0; jb < 4; ++jb) {
+#pragma unroll
+                            for (int c0 = 0; c0 < 2 * N; c0 += 16) {
+                                float o[16];
+                                const uint32_t addr = tmem + lane_base + L::TMEM_O + jb * 2 * N + c0;
+                                tmem_ld16(addr, o);
+                                tmem_wait_ld();
+#pragma unroll
+                                for (int c = 0; c < 16; ++c) o[c] *= f[(c0 + c) % N];
+                                tmem_st16(addr, o);
+                            }
+                        }
+                        tmem_wait_st();
+                        tc_fence_before();
+                    }
+                }
+                // P(g) may overwrite its buffer once PV(g-2) has completed
+                mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
+                if (tid == 0) TRACE(9, g);
+                uint8_t* pbuf = smem + L::OFF_P + sb * L::P_BUF_BYTES;
+#pragma unroll
+                for (int c0 = 0; c0 < N; c0 += 16) {
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        float pv[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int c = c0 + q4 * 4 + k;
+                            pv[k] = ex2(x[c]);                                        // ex2(-inf) = 0 for masked keys
+                            l_acc[c] += pv[k];
+                        }
+                        hi[q4] = pack_e4m3x4(pv[0], pv[1], pv[2], pv[3]);
+                        const float2 h01 = unpack_e4m3x2((uint16_t)(hi[q4] & 0xffffu)), h23 = unpack_e4m3x2((uint16_t)(hi[q4] >> 16));
+                        lo[q4] = pack_e4m3x4((pv[0] - h01.x) * 16.0f, (pv[1] - h01.y) * 16.0f,
+                                             (pv[2] - h23.x) * 16.0f, (pv[3] - h23.y) * 16.0f);
+                    }
+                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (TILE * 16) + tid * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (TILE * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                }
+                fence_proxy_async();
+                mbar_arrive(&ms.p_full[sb]);
+                if (tid == 0) TRACE(10, g);
+            }
+            // ---- epilogue of this (CTA, sequence) pair
+            {
+                const int gl = g0 + n_tiles - 1;
+                mbar_wait(&ms.p_empty[gl & 1], gl / 2, abort_flag);
+                if (tid == 0) TRACE(3, 63);
+                tc_fence_after();
+                reduce_cols(l_acc, false);
+                const bool whole = (t == seq_t0) && (my_t1 == seq_t1);
+                const int slot = w + b;
+                float inv[N];
+#pragma unroll
+                for (int c = 0; c < N; ++c) inv[c] = l_acc[c] > 0.0f ? __fdividef(out_scale, l_acc[c]) : 0.0f;
+                // one output element per (row, dim): this thread owns dims tid, 128+tid, ... of every row
+                const long long orow0 = whole ? ((long long)b * p.rows + row0) : ((long long)slot * p.rows + row0);
+                float* dst_f32 = whole ? p.out_o_f32 : p.part_o;
+                __nv_bfloat16* dst_bf16 = whole ? p.out : nullptr;
+                if (dst_f32) dst_f32 += orow0 * V_DIM + tid;
+                if (dst_bf16) dst_bf16 += orow0 * V_DIM + tid;
+#pragma unroll
+                for (int jb = 0; jb < 4; ++jb) {
+#pragma unroll
+                    for (int c0 = 0; c0 < N; c0 += 16) {
+                        float ohi[16], olo[16];
+                        tmem_ld16(tmem + lane_base + L::TMEM_O + jb * 2 * N + c0, ohi);
+                        tmem_ld16(tmem + lane_base + L::TMEM_O + jb * 2 * N + N + c0, olo);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) ohi[c] = fmaf(olo[c], 0.0625f, ohi[c]) * inv[c0 + c];
+                        if (dst_bf16) {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) dst_bf16[(c0 + c) * V_DIM + jb * 128] = __float2bfloat16_rn(ohi[c]);
+                        }
+                        if (dst_f32) {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) dst_f32[(c0 + c) * V_DIM + jb * 128] = ohi[c];
+                        }
+                    }
+                }
+                if (tid < N) {
+                    float lsum = 0.0f, nmc = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < N; ++c) if (c == tid) { lsum = l_acc[c]; nmc = nm[c]; }
+                    const float lse = lsum > 0.0f ? (log2f(lsum) - nmc) * LN2 : -INFINITY;
+                    if (whole) { if (p.out_lse) p.out_lse[(long long)b * p.rows + row0 + tid] = lse; }
+                    else p.part_lse[(long long)slot * p.rows + row0 + tid] = lse;
+                }
+                tc_fence_before();
+            }
+        }
+        g0 += n_tiles;
+        ++pair_idx;
+        t = my_t1;
+        __syncthreads();              // pair boundary: every role is drained
+        if (tid == 0) TRACE(4, 63);
+    }
+
+    __syncthreads();
+    if (tid == 0) TRACE(5, 63);
+    if (tid == 0 && ms.abort_flag) atomicMax(status, (int)ST_TIMEOUT);
+    if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem, L::TMEM_COLS); }
+}
+
+}  // namespace sm100
+
+bool sm100_supported(const MlaParams& p) {
+    return p.kv_format == KV_E4M3 && p.q_format == Q_E4M3 && p.rows % 16 == 0;
+}
+int sm100_rows_per_cta(const MlaParams& p) { return p.rows % 32 == 0 ? 32 : 16; }
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static cudaError_t make_row_gather_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, long long stride_bytes) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return e;
+        if (!fn || q != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+        encode = (EncodeTiledFn)fn;
+    }
+    // 2-D byte tensor [rows][row_bytes]; box = one row of 128 bytes (tile::gather4 fetches four such rows)
+    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)stride_bytes};
+    const cuuint32_t box[2] = {128, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <int N>
+static cudaError_t launch_n(const MlaParams& p, int* status, cudaStream_t stream) {
+    using L = sm100::Layout<N>;
+    const size_t smem = (size_t)L::OFF_MISC + sizeof(sm100::Misc) + (size_t)(p.batch + 1) * sizeof(int);
+    cudaError_t e = cudaFuncSetAttribute(sm100::mla_decode_sm100_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    // one tensor map per (cache base, rows, stride); re-encoded only when the cache changes
+    static thread_local CUtensorMap map;
+    static thread_local const void* m_base = nullptr;
+    static thread_local long long m_rows = -1, m_stride = -1;
+    if (m_base != p.kv_codes || m_rows != p.num_slots || m_stride != p.kv_codes_stride) {
+        e = make_row_gather_map(&map, p.kv_codes, p.num_slots, QK_DIM, p.kv_codes_stride);
+        if (e != cudaSuccess) return e;
+        m_base = p.kv_codes; m_rows = p.num_slots; m_stride = p.kv_codes_stride;
+    }
+    dim3 grid(p.num_ctas, p.rows / N);
+    sm100::mla_decode_sm100_kernel<N><<<grid, sm100::THREADS, smem, stream>>>(p, status, map);
+    return cudaGetLastError();
+}
+
+#ifdef B200MLA_TRACE
+extern "C" int b200_mla_debug_set_trace(long long* ptr) {
+    return (int)cudaMemcpyToSymbol(sm100::g_trace, &ptr, sizeof(ptr));
+}
+#endif
+
+cudaError_t launch_sm100(const MlaParams& p, int* status, cudaStream_t stream) {
+    return p.rows_per_cta == 32 ? launch_n<32>(p, status, stream) : launch_n<16>(p, status, stream);
+}
 
 }  // namespace b200mla

@@ -56,6 +56,7 @@ def _workspace(device, batch: int, heads: int, q_len: int) -> torch.Tensor:
         with torch.cuda.device(device):
             n = lib.b200_mla_workspace_bytes(batch, heads, q_len)
         ws = torch.empty(n, dtype=torch.uint8, device=device)
+        ws[:256].zero_()                      # kernel status word (sticky; 0 = no device-side wait ever expired)
         _workspace_cache[key] = ws
     return ws
 
@@ -83,7 +84,7 @@ def quantize_q_fp8(q: torch.Tensor):
 def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Tensor, *, sm_scale: float,
                q_len: int = 1, kv_indices=None, page_size: int = 1, kv_page_indptr=None, causal: bool = True,
                total_kv_hint: int = 0, kv_pos_offset=None, kv_total_len=None, return_partial: bool = False,
-               impl: str = "auto"):
+               impl: str = "auto", max_ctas: int = 0):
     """One decode call through b200_mla_decode.
 
     q         [batch*q_len, heads, 576] bf16, or float8_e4m3fn/uint8 codes with `q_scale` (f32[1])
@@ -105,6 +106,7 @@ def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Te
     a.batch, a.heads, a.q_len = batch, heads, q_len
     a.causal, a.page_size, a.impl = int(causal), page_size, _IMPLS[impl]
     a.sm_scale = float(sm_scale)
+    a.max_ctas = int(max_ctas)
     if q.dtype == torch.bfloat16:
         a.q_format = _cabi.Q_BF16
     elif q.dtype in (torch.float8_e4m3fn, torch.uint8):
@@ -203,4 +205,5 @@ def custom_kernel(data):
         q, q_scale, kv_format, kv_data[kv_format], kv_indptr,
         sm_scale=config["sm_scale"], q_len=q_len, kv_indices=config.get("kv_indices"),
         page_size=int(config.get("page_size", 1)), kv_page_indptr=config.get("kv_page_indptr"),
-        causal=bool(config.get("causal", True)), total_kv_hint=hint, impl=config.get("impl", "auto"))
+        causal=bool(config.get("causal", True)), total_kv_hint=hint, impl=config.get("impl", "auto"),
+        max_ctas=int(config.get("max_ctas", 0)))

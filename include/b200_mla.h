@@ -66,7 +66,7 @@ typedef struct {
     int32_t page_size;        /* tokens per page; kv_indices holds page ids. 1 for the reference layout */
     int32_t impl;             /* b200_mla_impl */
     float sm_scale;           /* softmax scale (reference: 1/sqrt(576), reference.py:46) */
-    int32_t reserved0;
+    int32_t max_ctas;         /* cap on stage-1 CTAs per row group; 0 = fill the device (tuning / tests) */
 
     /* ---- Q: [batch*q_len, heads, 576] ---- */
     const void *q;            /* device; bf16 or e4m3fn */
