@@ -10,32 +10,34 @@
 // split into two e4m3 terms (P = hi + lo/16, the two halves of the 2N columns) so that the
 // probabilities keep ~8 significant bits.
 //
-// Roles (192 threads):  warps 0-3  softmax / correction / epilogue (one TMEM lane per thread)
-//                       warp  4    tcgen05.mma issue (one lane), TMEM allocation
-//                       warp  5    paged gather by TMA: cp.async.bulk.tensor ... tile::gather4 fetches
-//                                  four cache rows named by the page table per instruction (4 x 128 B)
-//                                  straight into the 128B-swizzled UMMA layout; 160 instructions per
-//                                  128-token tile, completion counted in bytes on an mbarrier.
-//                                  (16-byte cp.async through the LSU topped out near 22 B/clk/SM.)
+// A 128-token tile is fetched and multiplied as two 64-token halves (QK MMAs with M = 64 write the
+// even half to TMEM lanes 0-15 and the odd half to lanes 16-31 of every 32-lane sub-partition), so
+// that the shared-memory ring holds four to five half tiles and the gather runs well ahead of the
+// math; softmax and the PV MMAs work on the whole 128-token tile.
+//
+// Roles:  warps 0-3  softmax / correction / epilogue (one TMEM lane = one token / one output dim per thread)
+//         warp  4    tcgen05.mma issue (one lane, event driven), TMEM allocation
+//         warps 5..  paged gather: 16-byte cp.async of cache rows through the page table straight
+//                    into the 128B-swizzled UMMA layout, completion signalled on an mbarrier.
+//                    (Rows of a page-size-1 table are not contiguous, so a tiled TMA box cannot fetch
+//                    them; the row-gather form of TMA, tile::gather4, was measured at ~60 cycles per
+//                    4-row instruction, 8.5 B/clk/SM, a third of what the copies below reach.)
 // Synchronisation is mbarrier based; every wait is bounded and on expiry sets a status word.
 // Online softmax runs in the exp2 domain with lazy re-centering: the reference maximum is only
 // raised (and O rescaled in TMEM) when a score exceeds it by more than 2^4.
 //
 // Role in the reference: the split-KV stage-1 kernels (mixed-mla/submission.py:122-250,
 // mixed-mla/versions/hip_mxfp4_v5/submission.py:214-656).
-#include <cuda.h>
-
 #include "mla_common.cuh"
 
 namespace b200mla {
 namespace sm100 {
 
-constexpr int TILE = 128;                 // tokens per tile = UMMA M
-constexpr int NS = 2;                     // cache tile stages
-constexpr int PANEL_BYTES = TILE * 128;   // one 128-byte-wide swizzled panel of a tile
+constexpr int TILE = 128;                 // tokens per schedule tile (softmax / PV granularity)
+constexpr int HALF = 64;                  // tokens per ring stage = UMMA M of the QK MMAs
+constexpr int PANEL_BYTES = HALF * 128;   // one 128-byte-wide swizzled panel of a half tile
 constexpr int NPANEL = 5;                 // 576 B per row = 4.5 panels (the last one half used)
 constexpr int STAGE_BYTES = NPANEL * PANEL_BYTES;
-constexpr int THREADS = 192;
 constexpr float RECENTER = 4.0f;          // log2 units
 constexpr float P_SCALE_LOG2 = 4.0f;      // probabilities are stored multiplied by 2^4
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // ~1 s: far beyond any legitimate wait of this kernel
@@ -102,16 +104,6 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Four rows (r0..r3) of a 2-D tensor, `box` bytes each starting at byte column x, land in four
-// consecutive 128-byte rows of shared memory with the tensor map's swizzle applied.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int r0, int r1, int r2, int r3) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
-}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
 }
@@ -178,10 +170,10 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 }
 // Same layout, start address moved by `bytes` (the address field never carries: smem < 256 KB).
 __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
-// Instruction descriptor, kind::f8f6f4: fp32 accumulate, e4m3 x e4m3, M = 128.
-__host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn_major, bool b_mn_major) {
+// Instruction descriptor, kind::f8f6f4: fp32 accumulate, e4m3 x e4m3.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_mn_major, bool b_mn_major) {
     return (1u << 4) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
-           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -201,6 +193,10 @@ __device__ __forceinline__ float2 unpack_e4m3x2(uint16_t v) { return __half22flo
 // ----------------------------------------------------------------------------------------------
 template <int N>
 struct Layout {
+    static constexpr int NS = (N == 16) ? 5 : 4;                 // ring stages (half tiles)
+    static constexpr int PRODUCER_WARPS = (N == 16) ? 4 : 2;     // fewer gather warps leave registers for N = 32
+    static constexpr int PRODUCERS = 32 * PRODUCER_WARPS;
+    static constexpr int THREADS = 160 + PRODUCERS;
     static constexpr int Q_BYTES = NPANEL * N * 128;
     static constexpr int P_CHUNKS = 2 * N / 16;                  // 16-column chunks of [hi | lo]
     static constexpr int P_BUF_BYTES = P_CHUNKS * TILE * 16;
@@ -212,17 +208,19 @@ struct Layout {
     static constexpr int TMEM_COLS = (10 * N <= 256) ? 256 : 512;
 };
 
+constexpr int MAX_NS = 5;
 struct Misc {
-    uint64_t kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], p_empty[2], q_full;
+    uint64_t kv_full[MAX_NS], kv_empty[MAX_NS], s_full[2], s_empty[2], p_full[2], p_empty[2], q_full;
     uint32_t tmem_base;
     int abort_flag;
+    int slot[MAX_NS][HALF];
     float red[4][32];            // cross-warp exchange (max / sum), 32 = max N
 };
 
 template <int N>
-__global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaParams p, int* status,
-                                                                      const __grid_constant__ CUtensorMap kv_map) {
+__global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel(const MlaParams p, int* status) {
     using L = Layout<N>;
+    constexpr int NS = L::NS, PRODUCERS = L::PRODUCERS, THREADS = L::THREADS;
     extern __shared__ __align__(1024) unsigned char smem[];
     Misc& ms = *reinterpret_cast<Misc*>(smem + L::OFF_MISC);
     int* prefix = reinterpret_cast<int*>(smem + L::OFF_MISC + sizeof(Misc));
@@ -234,9 +232,9 @@ __global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaP
     if (tid == 0) TRACE(0, 63);
 
     if (tid == 0) {
-        for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], 1); mbar_init(&ms.kv_empty[i], 1); }
+        for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], PRODUCERS); mbar_init(&ms.kv_empty[i], 1); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128);
+            mbar_init(&ms.s_full[i], 2); mbar_init(&ms.s_empty[i], 128);      // S: one commit per half
             mbar_init(&ms.p_full[i], 128); mbar_init(&ms.p_empty[i], 1);
         }
         mbar_init(&ms.q_full, 128);
@@ -276,92 +274,118 @@ __global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaP
         const int tot_len = p.kv_total_len ? p.kv_total_len[b] : seq_len;
         const int pos_first = (t - seq_t0) * TILE;
 
-        if (warp == 5) {
-            // =========================== paged gather by TMA (one warp) ===========================
-            // lane l owns tokens 4l..4l+3 of every tile: one gather4 per 128-byte panel of the row
-            auto slots_for = [&](int i, int (&sl)[4]) {
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int pos = pos_first + i * TILE + 4 * lane + u;
-                    // rows past the end of the sequence are fetched from an out-of-range row: zero fill
-                    sl[u] = pos < seq_len ? (int)slot_of(p, b, seq_base, page_base, pos) : (int)p.num_slots;
-                }
+        if (warp >= 5) {
+            // =========================== gather ===========================
+            // One ring stage = 64 tokens x 36 sixteen-byte columns.  Consecutive threads take
+            // consecutive columns, so a warp instruction reads 512 contiguous bytes of (at most two) rows.
+            const int pt = tid - 160;
+            const int n_half = 2 * n_tiles;
+            auto slot_for = [&](int hh) -> int {
+                const int pos = pos_first + hh * HALF + pt;
+                return (pt < HALF && pos < seq_len) ? (int)slot_of(p, b, seq_base, page_base, pos) : -1;
             };
-            int sl[4];
-            slots_for(0, sl);
-            for (int i = 0; i < n_tiles; ++i) {
-                const int g = g0 + i, st = g % NS;
-                mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
-                if (lane == 0) { TRACE(0, g); mbar_arrive_expect_tx(&ms.kv_full[st], STAGE_BYTES); }
-                __syncwarp();
-                const uint32_t dst = smem_base + st * STAGE_BYTES + lane * 512;
+            int my_slot = slot_for(0);
+            for (int hh = 0; hh < n_half; ++hh) {
+                const int gh = 2 * g0 + hh, st = gh % NS;
+                mbar_wait(&ms.kv_empty[st], gh / NS - 1, abort_flag);
+                if (pt < HALF) ms.slot[st][pt] = my_slot;
+                named_bar_sync(2, PRODUCERS);                   // slots of this half visible to every gather thread
+                if (pt == 0) TRACE(0, gh);
+                if (hh + 1 < n_half) my_slot = slot_for(hh + 1);
+                const uint32_t stage_addr = smem_base + st * STAGE_BYTES;
+                for (int id0 = pt; id0 < HALF * 36; id0 += 8 * PRODUCERS) {   // batches of 8: slots first, then the copies
+                    int sl[8];
 #pragma unroll
-                for (int j = 0; j < NPANEL; ++j)
-                    tma_gather4(dst + j * PANEL_BYTES, &kv_map, &ms.kv_full[st], j * 128, sl[0], sl[1], sl[2], sl[3]);
-                if (lane == 0) TRACE(1, g);
-                if (i + 1 < n_tiles) slots_for(i + 1, sl);
+                    for (int u = 0; u < 8; ++u) {
+                        const int id = id0 + u * PRODUCERS;
+                        sl[u] = id < HALF * 36 ? ms.slot[st][id / 36] : -2;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int id = id0 + u * PRODUCERS;
+                        if (sl[u] != -2) {
+                            const int tok = id / 36, c = id - tok * 36;
+                            const uint8_t* src = p.kv_codes + (long long)(sl[u] < 0 ? 0 : sl[u]) * p.kv_codes_stride + c * 16;
+                            const uint32_t dst = stage_addr + (c >> 3) * PANEL_BYTES + tok * 128 + (((c & 7) ^ (tok & 7)) << 4);
+                            cp_async16(dst, src, sl[u] < 0 ? 0u : 16u);     // rows past the end of the sequence: zero fill
+                        }
+                    }
+                }
+                if (pt == 0) TRACE(1, gh);
+                cp_async_mbar_arrive_noinc(&ms.kv_full[st]);   // asynchronous: the thread does not wait for its copies
             }
+            cp_async_wait_all();                               // nothing of this pair is in flight past the pair boundary
         } else if (warp == 4) {
             // =========================== MMA issue (one lane) ===========================
             if (lane == 0) {
-                constexpr uint32_t IDESC_QK = make_idesc(N, false, false);
-                constexpr uint32_t IDESC_PV = make_idesc(2 * N, true, true);
+                constexpr uint32_t IDESC_QK = make_idesc(HALF, N, false, false);
+                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
                 // descriptor bases; per-MMA descriptors differ only in the start address
                 const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                  // + stage
                 const uint64_t d_qk_b = make_desc(smem_base + L::OFF_Q, 16, 1024, SWIZZLE_128B);
                 const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
                 const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, TILE * 16, SWIZZLE_NONE); // + buffer
-                auto issue_pv = [&](int g, bool first) {
-                    const int st = g % NS, pb = g & 1;
-                    TRACE(4, g);
-                    tc_fence_after();
-                    const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
-                    const uint64_t b0 = desc_advance(d_pv_b, pb * L::P_BUF_BYTES);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            umma_f8(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
-                                    desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
-                        }
-                    }
-                    umma_commit(&ms.kv_empty[st]);
-                    umma_commit(&ms.p_empty[pb]);
-                    TRACE(5, g);
-                };
-                auto issue_qk = [&](int g) {
-                    const int st = g % NS, sb = g & 1;
-                    TRACE(2, g);
+                // S^T half: 64 tokens x N, rows 16k..16k+15 land in TMEM lanes 32k..32k+15 (+16 for the odd half)
+                auto issue_qk = [&](int hq) {
+                    const int g = g0 + (hq >> 1), gh = 2 * g0 + hq, st = gh % NS, sb = g & 1;
+                    TRACE(2, gh);
+                    fence_proxy_async();       // the stage was written by cp.async (generic proxy); the MMA reads it through the async proxy
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_qk_a, st * STAGE_BYTES);
+                    const uint32_t d = tmem + L::TMEM_S + sb * N + ((hq & 1) ? (16u << 16) : 0u);
 #pragma unroll
                     for (int k = 0; k < 18; ++k) {
-                        umma_f8(tmem + L::TMEM_S + sb * N, desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32),
+                        umma_f8(d, desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32),
                                 desc_advance(d_qk_b, (k >> 2) * (N * 128) + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
                     }
                     umma_commit(&ms.s_full[sb]);
-                    TRACE(3, g);
+                    TRACE(3, gh);
                 };
-                // Event driven: PV(g) as soon as P(g) is published (it frees the tile for the next gather),
-                // else QK of the next tile as soon as that tile has landed and its S buffer is free.
+                // O^T += V^T P^T over the 128 tokens of tile g (two ring stages), four blocks of 128 dims
+                auto issue_pv = [&](int i) {
+                    const int g = g0 + i, pb = g & 1;
+                    TRACE(4, 2 * g);
+                    tc_fence_after();
+                    const uint64_t b0 = desc_advance(d_pv_b, pb * L::P_BUF_BYTES);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int st = (2 * g + half) % NS;
+                        const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                            for (int kk = 0; kk < 2; ++kk) {
+                                umma_f8(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
+                                        desc_advance(b0, (half * 2 + kk) * 32 * 16), IDESC_PV,
+                                        (i == 0 && half == 0 && kk == 0) ? 0u : 1u);
+                            }
+                        }
+                        umma_commit(&ms.kv_empty[st]);
+                    }
+                    umma_commit(&ms.p_empty[pb]);
+                    TRACE(5, 2 * g);
+                };
                 mbar_wait(&ms.q_full, pair_idx, abort_flag);   // Q of this sequence is in shared memory
+                // Event driven: PV(g) as soon as P(g) is published (it frees two ring stages for the gather),
+                // else QK of the next half as soon as it has landed and (for an even half) its S buffer is free.
+                const int n_half = 2 * n_tiles;
                 int nq = 0, nv = 0;
                 long long t_idle = clock64();
                 uint32_t spins = 0;
                 while (nv < n_tiles) {
-                    const int gv = g0 + nv, gq = g0 + nq;
-                    if (nv < nq && mbar_try_nb(&ms.p_full[gv & 1], (uint32_t)(gv / 2) & 1u)) {
-                        issue_pv(gv, nv == 0);
+                    const int gv = g0 + nv, gq = g0 + (nq >> 1), ghq = 2 * g0 + nq;
+                    if (2 * nv + 2 <= nq && mbar_try_nb(&ms.p_full[gv & 1], (uint32_t)(gv / 2) & 1u)) {
+                        issue_pv(nv);
                         ++nv; spins = 0;
-                    } else if (nq < n_tiles && mbar_try_nb(&ms.kv_full[gq % NS], (uint32_t)(gq / NS) & 1u) &&
-                               mbar_try_nb(&ms.s_empty[gq & 1], (uint32_t)(gq / 2 - 1) & 1u)) {
-                        issue_qk(gq);
+                    } else if (nq < n_half && mbar_try_nb(&ms.kv_full[ghq % NS], (uint32_t)(ghq / NS) & 1u) &&
+                               ((nq & 1) || mbar_try_nb(&ms.s_empty[gq & 1], (uint32_t)(gq / 2 - 1) & 1u))) {
+                        issue_qk(nq);
                         ++nq; spins = 0;
                     } else if ((++spins & 63u) == 0u) {
                         if (spins == 64u) t_idle = clock64();
                         if (*abort_flag || clock64() - t_idle > WAIT_LIMIT_CYCLES) {
                             *abort_flag = 1;                    // give up waiting; issue the rest regardless so that every commit still arrives
-                            if (nq < n_tiles) { issue_qk(gq); ++nq; } else { issue_pv(gv, nv == 0); ++nv; }
+                            if (nq < n_half) { issue_qk(nq); ++nq; } else { issue_pv(nv); ++nv; }
                         }
                     }
                 }
@@ -369,6 +393,8 @@ __global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaP
         } else {
             // =========================== softmax / correction / epilogue (128 threads) ===========
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+            // token of this thread inside a 128-token tile (see the QK lane mapping above)
+            const int tok = (lane >> 4) * HALF + 16 * warp + (lane & 15);
             // ---- Q rows of this sequence -> swizzled K-major panels, published to the MMA warp
             // (the previous pair's MMAs have all completed: its epilogue waited for the last PV)
             for (int i = tid; i < N * 36; i += 128) {
@@ -419,7 +445,7 @@ __global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaP
             for (int i = 0; i < n_tiles; ++i) {
                 const int g = g0 + i, sb = g & 1;
                 mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
-                if (tid == 0) TRACE(6, g);
+                if (tid == 0) TRACE(6, 2 * g);
                 tc_fence_after();
                 float s[N];
 #pragma unroll
@@ -429,7 +455,7 @@ __global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaP
                 mbar_arrive(&ms.s_empty[sb]);
 
                 // x = log2-domain exponent of the stored probability: score*scale - m_ref + P_SCALE_LOG2
-                const int pos = pos_first + i * TILE + tid;
+                const int pos = pos_first + i * TILE + tok;
                 const bool masked_tile = pos_first + (i + 1) * TILE > lim_min;       // uniform
                 float x[N];
 #pragma unroll
@@ -441,9 +467,9 @@ __global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaP
                 float xm = x[0];
 #pragma unroll
                 for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
-                if (tid == 0) TRACE(7, g);
+                if (tid == 0) TRACE(7, 2 * g);
                 const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
-                if (tid == 0) TRACE(8, g);
+                if (tid == 0) TRACE(8, 2 * g);
                 if (recenter) {
                     float mx[N];
 #pragma unroll
@@ -484,7 +510,7 @@ __global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaP
                 }
                 // P(g) may overwrite its buffer once PV(g-2) has completed
                 mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
-                if (tid == 0) TRACE(9, g);
+                if (tid == 0) TRACE(9, 2 * g);
                 uint8_t* pbuf = smem + L::OFF_P + sb * L::P_BUF_BYTES;
 #pragma unroll
                 for (int c0 = 0; c0 < N; c0 += 16) {
@@ -503,12 +529,12 @@ __global__ void __launch_bounds__(THREADS, 1) mla_decode_sm100_kernel(const MlaP
                         lo[q4] = pack_e4m3x4((pv[0] - h01.x) * 16.0f, (pv[1] - h01.y) * 16.0f,
                                              (pv[2] - h23.x) * 16.0f, (pv[3] - h23.y) * 16.0f);
                     }
-                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (TILE * 16) + tid * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (TILE * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (TILE * 16) + tok * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (TILE * 16) + tok * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
                 fence_proxy_async();
                 mbar_arrive(&ms.p_full[sb]);
-                if (tid == 0) TRACE(10, g);
+                if (tid == 0) TRACE(10, 2 * g);
             }
             // ---- epilogue of this (CTA, sequence) pair
             {
@@ -579,31 +605,11 @@ bool sm100_supported(const MlaParams& p) {
 }
 int sm100_rows_per_cta(const MlaParams& p) { return p.rows % 32 == 0 ? 32 : 16; }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static cudaError_t make_row_gather_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, long long stride_bytes) {
-    static EncodeTiledFn encode = nullptr;
-    if (!encode) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-        if (e != cudaSuccess) return e;
-        if (!fn || q != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
-        encode = (EncodeTiledFn)fn;
-    }
-    // 2-D byte tensor [rows][row_bytes]; box = one row of 128 bytes (tile::gather4 fetches four such rows)
-    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)stride_bytes};
-    const cuuint32_t box[2] = {128, 1};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+#ifdef B200MLA_TRACE
+extern "C" int b200_mla_debug_set_trace(long long* ptr) {
+    return (int)cudaMemcpyToSymbol(sm100::g_trace, &ptr, sizeof(ptr));
 }
+#endif
 
 template <int N>
 static cudaError_t launch_n(const MlaParams& p, int* status, cudaStream_t stream) {
@@ -611,25 +617,10 @@ static cudaError_t launch_n(const MlaParams& p, int* status, cudaStream_t stream
     const size_t smem = (size_t)L::OFF_MISC + sizeof(sm100::Misc) + (size_t)(p.batch + 1) * sizeof(int);
     cudaError_t e = cudaFuncSetAttribute(sm100::mla_decode_sm100_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    // one tensor map per (cache base, rows, stride); re-encoded only when the cache changes
-    static thread_local CUtensorMap map;
-    static thread_local const void* m_base = nullptr;
-    static thread_local long long m_rows = -1, m_stride = -1;
-    if (m_base != p.kv_codes || m_rows != p.num_slots || m_stride != p.kv_codes_stride) {
-        e = make_row_gather_map(&map, p.kv_codes, p.num_slots, QK_DIM, p.kv_codes_stride);
-        if (e != cudaSuccess) return e;
-        m_base = p.kv_codes; m_rows = p.num_slots; m_stride = p.kv_codes_stride;
-    }
     dim3 grid(p.num_ctas, p.rows / N);
-    sm100::mla_decode_sm100_kernel<N><<<grid, sm100::THREADS, smem, stream>>>(p, status, map);
+    sm100::mla_decode_sm100_kernel<N><<<grid, L::THREADS, smem, stream>>>(p, status);
     return cudaGetLastError();
 }
-
-#ifdef B200MLA_TRACE
-extern "C" int b200_mla_debug_set_trace(long long* ptr) {
-    return (int)cudaMemcpyToSymbol(sm100::g_trace, &ptr, sizeof(ptr));
-}
-#endif
 
 cudaError_t launch_sm100(const MlaParams& p, int* status, cudaStream_t stream) {
     return p.rows_per_cta == 32 ? launch_n<32>(p, status, stream) : launch_n<16>(p, status, stream);
