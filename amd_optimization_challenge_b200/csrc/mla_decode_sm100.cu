@@ -10,18 +10,21 @@
 // split into two e4m3 terms (P = hi + lo/16, the two halves of the 2N columns) so that the
 // probabilities keep ~8 significant bits.
 //
-// A 128-token tile is fetched and multiplied as two 64-token halves (QK MMAs with M = 64 write the
-// even half to TMEM lanes 0-15 and the odd half to lanes 16-31 of every 32-lane sub-partition), so
-// that the shared-memory ring holds four to five half tiles and the gather runs well ahead of the
-// math; softmax and the PV MMAs work on the whole 128-token tile.
+// The CTA walks its span of 128-token tiles as one continuous stream: the gather, the MMA issue and
+// the softmax each run their own loop over the tiles and meet only through mbarriers, also across
+// the boundary between two sequences (Q is double buffered; only the first PV of the next sequence
+// waits until the epilogue has read O out of TMEM).
 //
 // Roles:  warps 0-3  softmax / correction / epilogue (one TMEM lane = one token / one output dim per thread)
 //         warp  4    tcgen05.mma issue (one lane, event driven), TMEM allocation
-//         warps 5..  paged gather: 16-byte cp.async of cache rows through the page table straight
-//                    into the 128B-swizzled UMMA layout, completion signalled on an mbarrier.
-//                    (Rows of a page-size-1 table are not contiguous, so a tiled TMA box cannot fetch
-//                    them; the row-gather form of TMA, tile::gather4, was measured at ~60 cycles per
-//                    4-row instruction, 8.5 B/clk/SM, a third of what the copies below reach.)
+//         warps 5..  paged gather: 16-byte cp.async of cache rows (and of Q) through the page table
+//                    straight into the 128B-swizzled UMMA layout, completion signalled on an mbarrier.
+// Movers measured on B200 for shuffled 576-byte rows, device-wide, one CTA per SM:
+//         16-byte cp.async (LSU)                       3.5 - 4.4 TB/s, lands directly in operand layout
+//         TMA tile::gather4 (4 rows x 128 B / instr)   1.3 - 2.9 TB/s, ~60 cycles per instruction
+//         one cp.async.bulk per row, 4 issuing warps   5.3 TB/s, but row-major: needs ~80 KB of raw staging
+//                                                      per SM beside the operand tiles plus a re-layout pass
+// A tiled TMA box cannot fetch the rows of a page-size-1 table (they are not contiguous).
 // Synchronisation is mbarrier based; every wait is bounded and on expiry sets a status word.
 // Online softmax runs in the exp2 domain with lazy re-centering: the reference maximum is only
 // raised (and O rescaled in TMEM) when a score exceeds it by more than 2^4.
@@ -33,9 +36,9 @@
 namespace b200mla {
 namespace sm100 {
 
-constexpr int TILE = 128;                 // tokens per schedule tile (softmax / PV granularity)
-constexpr int HALF = 64;                  // tokens per ring stage = UMMA M of the QK MMAs
-constexpr int PANEL_BYTES = HALF * 128;   // one 128-byte-wide swizzled panel of a half tile
+constexpr int TILE = 128;                 // tokens per tile = UMMA M
+constexpr int NS = 2;                     // cache tile stages
+constexpr int PANEL_BYTES = TILE * 128;   // one 128-byte-wide swizzled panel of a tile
 constexpr int NPANEL = 5;                 // 576 B per row = 4.5 panels (the last one half used)
 constexpr int STAGE_BYTES = NPANEL * PANEL_BYTES;
 constexpr float RECENTER = 4.0f;          // log2 units
@@ -47,7 +50,8 @@ enum { ST_OK = 0, ST_TIMEOUT = 1 };
 // Optional timeline instrumentation (compiled in only with -DB200MLA_TRACE; development aid).
 #ifdef B200MLA_TRACE
 __device__ long long* g_trace = nullptr;
-#define TRACE(id, tile) do { if (g_trace && blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_trace[(tile) * 16 + (id)] = clock64(); } while (0)
+#define TRACE(id, tile) do { if (g_trace && blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_trace[(tile) * 16 + (id)] = clock64(); \
+    if (g_trace && (tile) == 63 && ((id) == 0 || (id) == 5)) { unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt)); g_trace[1024 + blockIdx.x * 2 + ((id) == 5)] = (long long)gt; } } while (0)
 #else
 #define TRACE(id, tile) do { } while (0)
 #endif
@@ -193,34 +197,62 @@ __device__ __forceinline__ float2 unpack_e4m3x2(uint16_t v) { return __half22flo
 // ----------------------------------------------------------------------------------------------
 template <int N>
 struct Layout {
-    static constexpr int NS = (N == 16) ? 5 : 4;                 // ring stages (half tiles)
-    static constexpr int PRODUCER_WARPS = (N == 16) ? 4 : 2;     // fewer gather warps leave registers for N = 32
+    static constexpr int PRODUCER_WARPS = (N == 16) ? 8 : 2;     // fewer gather warps leave registers for N = 32
     static constexpr int PRODUCERS = 32 * PRODUCER_WARPS;
     static constexpr int THREADS = 160 + PRODUCERS;
-    static constexpr int Q_BYTES = NPANEL * N * 128;
+    static constexpr int Q_PANEL_BYTES = N * 128;
+    static constexpr int Q_BYTES = NPANEL * Q_PANEL_BYTES;        // one Q buffer (two of them: next sequence's Q loads early)
     static constexpr int P_CHUNKS = 2 * N / 16;                  // 16-column chunks of [hi | lo]
     static constexpr int P_BUF_BYTES = P_CHUNKS * TILE * 16;
     static constexpr int OFF_Q = NS * STAGE_BYTES;
-    static constexpr int OFF_P = OFF_Q + Q_BYTES;
+    static constexpr int OFF_P = OFF_Q + 2 * Q_BYTES;
     static constexpr int OFF_MISC = OFF_P + 2 * P_BUF_BYTES;
     static constexpr int TMEM_S = 0;                              // two S buffers of N columns
     static constexpr int TMEM_O = 2 * N;                          // four O blocks of 2N columns
     static constexpr int TMEM_COLS = (10 * N <= 256) ? 256 : 512;
 };
 
-constexpr int MAX_NS = 5;
 struct Misc {
-    uint64_t kv_full[MAX_NS], kv_empty[MAX_NS], s_full[2], s_empty[2], p_full[2], p_empty[2], q_full;
+    uint64_t kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], p_empty[2];
+    uint64_t q_full[2], q_empty[2], o_free;
     uint32_t tmem_base;
     int abort_flag;
-    int slot[MAX_NS][HALF];
+    int slot[NS][TILE];
     float red[4][32];            // cross-warp exchange (max / sum), 32 = max N
+};
+
+// Position of one role inside the CTA's span of global tiles [t_begin, t_end): which sequence the
+// current tile belongs to, and that sequence's geometry.  Every role walks the span with its own copy.
+struct Walker {
+    int b, seq_t0, seq_t1;                  // sequence and its global tile range
+    int seq_base, seq_len, page_base, pos_off, tot_len;
+    int pair;                               // (CTA, sequence) pairs started so far, minus one
+    __device__ __forceinline__ void init(const int* prefix, int batch, int t_begin) {
+        b = seq_of_tile(prefix, batch, t_begin) - 1;
+        seq_t1 = -1;
+        pair = -1;
+    }
+    // Make the walker describe the sequence that owns global tile t (t only grows between calls).
+    // Returns true when t is the first tile of a new (CTA, sequence) pair.
+    __device__ __forceinline__ bool seek(const MlaParams& p, const int* prefix, int t) {
+        if (t < seq_t1) return false;
+        do { ++b; } while (prefix[b + 1] <= t);
+        seq_t0 = prefix[b];
+        seq_t1 = prefix[b + 1];
+        seq_base = p.kv_indptr[b];
+        seq_len = p.kv_indptr[b + 1] - seq_base;
+        page_base = p.kv_page_indptr ? p.kv_page_indptr[b] : seq_base;
+        pos_off = p.kv_pos_offset ? p.kv_pos_offset[b] : 0;
+        tot_len = p.kv_total_len ? p.kv_total_len[b] : seq_len;
+        ++pair;
+        return true;
+    }
 };
 
 template <int N>
 __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel(const MlaParams p, int* status) {
     using L = Layout<N>;
-    constexpr int NS = L::NS, PRODUCERS = L::PRODUCERS, THREADS = L::THREADS;
+    constexpr int PRODUCERS = L::PRODUCERS, THREADS = L::THREADS;
     extern __shared__ __align__(1024) unsigned char smem[];
     Misc& ms = *reinterpret_cast<Misc*>(smem + L::OFF_MISC);
     int* prefix = reinterpret_cast<int*>(smem + L::OFF_MISC + sizeof(Misc));
@@ -234,10 +266,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], PRODUCERS); mbar_init(&ms.kv_empty[i], 1); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&ms.s_full[i], 2); mbar_init(&ms.s_empty[i], 128);      // S: one commit per half
+            mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128);
             mbar_init(&ms.p_full[i], 128); mbar_init(&ms.p_empty[i], 1);
+            mbar_init(&ms.q_full[i], PRODUCERS); mbar_init(&ms.q_empty[i], 1);
         }
-        mbar_init(&ms.q_full, 128);
+        mbar_init(&ms.o_free, 128);
         ms.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -251,54 +284,66 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
         for (int i = tid; i <= p.batch; i += THREADS) p.tile_prefix[i] = prefix[i];
 
     const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
+    const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
 
     const float q_sc = __ldg(p.q_scale), kv_sc = __ldg(p.kv_scale);
     const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
     const float out_scale = kv_sc;
     volatile int* abort_flag = &ms.abort_flag;
 
-    int g0 = 0;                       // tiles processed so far by this CTA (drives stages and phases)
-    int pair_idx = 0;                 // (CTA, sequence) pairs processed so far
-    int b = t_begin < t_end ? seq_of_tile(prefix, p.batch, t_begin) : 0;
-    int t = t_begin;
-    while (t < t_end) {
-        if (*abort_flag) break;       // uniform: read right after a __syncthreads()
-        while (prefix[b + 1] <= t) ++b;
-        const int seq_t0 = prefix[b], seq_t1 = prefix[b + 1];
-        const int my_t1 = min(t_end, seq_t1);
-        const int n_tiles = my_t1 - t;
-        const int seq_base = p.kv_indptr[b];
-        const int seq_len = p.kv_indptr[b + 1] - seq_base;
-        const int page_base = p.kv_page_indptr ? p.kv_page_indptr[b] : seq_base;
-        const int pos_off = p.kv_pos_offset ? p.kv_pos_offset[b] : 0;
-        const int tot_len = p.kv_total_len ? p.kv_total_len[b] : seq_len;
-        const int pos_first = (t - seq_t0) * TILE;
-
+    if (n_total > 0) {
         if (warp >= 5) {
             // =========================== gather ===========================
-            // One ring stage = 64 tokens x 36 sixteen-byte columns.  Consecutive threads take
-            // consecutive columns, so a warp instruction reads 512 contiguous bytes of (at most two) rows.
+            // One stage = 128 tokens x 36 sixteen-byte columns.  Consecutive threads take consecutive
+            // columns, so a warp instruction reads 512 contiguous bytes of (at most two) rows.
             const int pt = tid - 160;
-            const int n_half = 2 * n_tiles;
-            auto slot_for = [&](int hh) -> int {
-                const int pos = pos_first + hh * HALF + pt;
-                return (pt < HALF && pos < seq_len) ? (int)slot_of(p, b, seq_base, page_base, pos) : -1;
+            Walker wk; wk.init(prefix, p.batch, t_begin);
+            Walker wn = wk;                                       // one tile ahead, for the page-table prefetch
+            // thread pt looks up the page table for tokens pt, pt + PRODUCERS, ... of a tile (-1 past the end)
+            constexpr int SLOTS_PER_THREAD = (TILE + PRODUCERS - 1) / PRODUCERS;
+            int my_slot[SLOTS_PER_THREAD];
+            auto slots_for = [&](int g) {
+                if (g < n_total) wn.seek(p, prefix, t_begin + g);
+#pragma unroll
+                for (int k = 0; k < SLOTS_PER_THREAD; ++k) {
+                    const int tok = pt + k * PRODUCERS;
+                    const int pos = (t_begin + g - wn.seq_t0) * TILE + tok;
+                    my_slot[k] = (g < n_total && tok < TILE && pos < wn.seq_len)
+                                     ? (int)slot_of(p, wn.b, wn.seq_base, wn.page_base, pos) : -1;
+                }
             };
-            int my_slot = slot_for(0);
-            for (int hh = 0; hh < n_half; ++hh) {
-                const int gh = 2 * g0 + hh, st = gh % NS;
-                mbar_wait(&ms.kv_empty[st], gh / NS - 1, abort_flag);
-                if (pt < HALF) ms.slot[st][pt] = my_slot;
-                named_bar_sync(2, PRODUCERS);                   // slots of this half visible to every gather thread
-                if (pt == 0) TRACE(0, gh);
-                if (hh + 1 < n_half) my_slot = slot_for(hh + 1);
+            slots_for(0);
+            for (int g = 0; g < n_total; ++g) {
+                const int st = g % NS;
+                const bool first = wk.seek(p, prefix, t_begin + g);
+                if (first) {
+                    // Q rows of the new sequence -> swizzled K-major panels of Q buffer (pair & 1)
+                    const int qb = wk.pair & 1;
+                    mbar_wait(&ms.q_empty[qb], wk.pair / 2 - 1, abort_flag);
+                    const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
+                    for (int i = pt; i < N * 36; i += PRODUCERS) {
+                        const int r = i / 36, c = i - r * 36;
+                        const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
+                                             (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
+                        cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
+                    }
+                    cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
+                }
+                mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
+#pragma unroll
+                for (int k = 0; k < SLOTS_PER_THREAD; ++k)
+                    if (pt + k * PRODUCERS < TILE) ms.slot[st][pt + k * PRODUCERS] = my_slot[k];
+                named_bar_sync(2, PRODUCERS);                   // slots of this tile visible to every gather thread
+                if (pt == 0) TRACE(0, g);
+                slots_for(g + 1);
                 const uint32_t stage_addr = smem_base + st * STAGE_BYTES;
-                for (int id0 = pt; id0 < HALF * 36; id0 += 8 * PRODUCERS) {   // batches of 8: slots first, then the copies
+                for (int id0 = pt; id0 < TILE * 36; id0 += 8 * PRODUCERS) {   // batches of 8: slots first, then the copies
                     int sl[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         const int id = id0 + u * PRODUCERS;
-                        sl[u] = id < HALF * 36 ? ms.slot[st][id / 36] : -2;
+                        sl[u] = id < TILE * 36 ? ms.slot[st][id / 36] : -2;
                     }
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
@@ -311,117 +356,101 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         }
                     }
                 }
-                if (pt == 0) TRACE(1, gh);
+                if (pt == 0) TRACE(1, g);
                 cp_async_mbar_arrive_noinc(&ms.kv_full[st]);   // asynchronous: the thread does not wait for its copies
             }
-            cp_async_wait_all();                               // nothing of this pair is in flight past the pair boundary
+            cp_async_wait_all();
         } else if (warp == 4) {
             // =========================== MMA issue (one lane) ===========================
             if (lane == 0) {
-                constexpr uint32_t IDESC_QK = make_idesc(HALF, N, false, false);
+                constexpr uint32_t IDESC_QK = make_idesc(TILE, N, false, false);
                 constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
                 // descriptor bases; per-MMA descriptors differ only in the start address
                 const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                  // + stage
-                const uint64_t d_qk_b = make_desc(smem_base + L::OFF_Q, 16, 1024, SWIZZLE_128B);
+                const uint64_t d_qk_b = make_desc(smem_base + L::OFF_Q, 16, 1024, SWIZZLE_128B);       // + Q buffer
                 const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
                 const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, TILE * 16, SWIZZLE_NONE); // + buffer
-                // S^T half: 64 tokens x N, rows 16k..16k+15 land in TMEM lanes 32k..32k+15 (+16 for the odd half)
-                auto issue_qk = [&](int hq) {
-                    const int g = g0 + (hq >> 1), gh = 2 * g0 + hq, st = gh % NS, sb = g & 1;
-                    TRACE(2, gh);
-                    fence_proxy_async();       // the stage was written by cp.async (generic proxy); the MMA reads it through the async proxy
+                Walker wq, wv;                                    // the QK stream runs ahead of the PV stream
+                wq.init(prefix, p.batch, t_begin);
+                wv = wq;
+                // S^T[128 tok x N] = K . Q^T for tile g
+                auto issue_qk = [&](int g) {
+                    const int st = g % NS, sb = g & 1;
+                    TRACE(2, g);
+                    fence_proxy_async();       // stage and Q were written by cp.async (generic proxy); the MMA reads through the async proxy
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_qk_a, st * STAGE_BYTES);
-                    const uint32_t d = tmem + L::TMEM_S + sb * N + ((hq & 1) ? (16u << 16) : 0u);
+                    const uint64_t b0 = desc_advance(d_qk_b, (wq.pair & 1) * L::Q_BYTES);
 #pragma unroll
                     for (int k = 0; k < 18; ++k) {
-                        umma_f8(d, desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32),
-                                desc_advance(d_qk_b, (k >> 2) * (N * 128) + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
+                        umma_f8(tmem + L::TMEM_S + sb * N, desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32),
+                                desc_advance(b0, (k >> 2) * L::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
                     }
                     umma_commit(&ms.s_full[sb]);
-                    TRACE(3, gh);
+                    // last tile of this (CTA, sequence) pair: its Q buffer is free once these MMAs have run
+                    if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit(&ms.q_empty[wq.pair & 1]);
+                    TRACE(3, g);
                 };
-                // O^T += V^T P^T over the 128 tokens of tile g (two ring stages), four blocks of 128 dims
-                auto issue_pv = [&](int i) {
-                    const int g = g0 + i, pb = g & 1;
-                    TRACE(4, 2 * g);
+                // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
+                auto issue_pv = [&](int g, bool first) {
+                    const int st = g % NS, pb = g & 1;
+                    TRACE(4, g);
                     tc_fence_after();
+                    const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
                     const uint64_t b0 = desc_advance(d_pv_b, pb * L::P_BUF_BYTES);
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int st = (2 * g + half) % NS;
-                        const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
+                    for (int j = 0; j < 4; ++j) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-#pragma unroll
-                            for (int kk = 0; kk < 2; ++kk) {
-                                umma_f8(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
-                                        desc_advance(b0, (half * 2 + kk) * 32 * 16), IDESC_PV,
-                                        (i == 0 && half == 0 && kk == 0) ? 0u : 1u);
-                            }
+                        for (int kk = 0; kk < 4; ++kk) {
+                            umma_f8(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
+                                    desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
                         }
-                        umma_commit(&ms.kv_empty[st]);
                     }
+                    umma_commit(&ms.kv_empty[st]);
                     umma_commit(&ms.p_empty[pb]);
-                    TRACE(5, 2 * g);
+                    TRACE(5, g);
                 };
-                mbar_wait(&ms.q_full, pair_idx, abort_flag);   // Q of this sequence is in shared memory
-                // Event driven: PV(g) as soon as P(g) is published (it frees two ring stages for the gather),
-                // else QK of the next half as soon as it has landed and (for an even half) its S buffer is free.
-                const int n_half = 2 * n_tiles;
+                // Event driven: PV(g) as soon as P(g) is published (it frees the tile for the gather), else
+                // QK of the next tile as soon as it has landed, its S buffer is free and its Q is in place.
                 int nq = 0, nv = 0;
+                bool q_first = wq.seek(p, prefix, t_begin), v_first = wv.seek(p, prefix, t_begin);
                 long long t_idle = clock64();
                 uint32_t spins = 0;
-                while (nv < n_tiles) {
-                    const int gv = g0 + nv, gq = g0 + (nq >> 1), ghq = 2 * g0 + nq;
-                    if (2 * nv + 2 <= nq && mbar_try_nb(&ms.p_full[gv & 1], (uint32_t)(gv / 2) & 1u)) {
-                        issue_pv(nv);
-                        ++nv; spins = 0;
-                    } else if (nq < n_half && mbar_try_nb(&ms.kv_full[ghq % NS], (uint32_t)(ghq / NS) & 1u) &&
-                               ((nq & 1) || mbar_try_nb(&ms.s_empty[gq & 1], (uint32_t)(gq / 2 - 1) & 1u))) {
-                        issue_qk(nq);
-                        ++nq; spins = 0;
-                    } else if ((++spins & 63u) == 0u) {
+                while (nv < n_total) {
+                    bool pv_ready = nv < nq && mbar_try_nb(&ms.p_full[nv & 1], (uint32_t)(nv / 2) & 1u);
+                    // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
+                    if (pv_ready && v_first && wv.pair > 0) pv_ready = mbar_try_nb(&ms.o_free, (uint32_t)(wv.pair - 1) & 1u);
+                    bool qk_ready = !pv_ready && nq < n_total &&
+                                    mbar_try_nb(&ms.kv_full[nq % NS], (uint32_t)(nq / NS) & 1u) &&
+                                    mbar_try_nb(&ms.s_empty[nq & 1], (uint32_t)(nq / 2 - 1) & 1u);
+                    if (qk_ready && q_first) qk_ready = mbar_try_nb(&ms.q_full[wq.pair & 1], (uint32_t)(wq.pair / 2) & 1u);
+                    if (!pv_ready && !qk_ready && (++spins & 63u) == 0u) {
                         if (spins == 64u) t_idle = clock64();
                         if (*abort_flag || clock64() - t_idle > WAIT_LIMIT_CYCLES) {
-                            *abort_flag = 1;                    // give up waiting; issue the rest regardless so that every commit still arrives
-                            if (nq < n_half) { issue_qk(nq); ++nq; } else { issue_pv(nv); ++nv; }
+                            *abort_flag = 1;        // give up waiting; issue the rest regardless so that every commit still arrives
+                            if (nq < n_total) qk_ready = true; else pv_ready = true;
                         }
+                    }
+                    if (pv_ready) {
+                        issue_pv(nv, v_first);
+                        ++nv; spins = 0;
+                        if (nv < n_total) v_first = wv.seek(p, prefix, t_begin + nv);
+                    } else if (qk_ready) {
+                        issue_qk(nq);
+                        ++nq; spins = 0;
+                        if (nq < n_total) q_first = wq.seek(p, prefix, t_begin + nq);
                     }
                 }
             }
         } else {
             // =========================== softmax / correction / epilogue (128 threads) ===========
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-            // token of this thread inside a 128-token tile (see the QK lane mapping above)
-            const int tok = (lane >> 4) * HALF + 16 * warp + (lane & 15);
-            // ---- Q rows of this sequence -> swizzled K-major panels, published to the MMA warp
-            // (the previous pair's MMAs have all completed: its epilogue waited for the last PV)
-            for (int i = tid; i < N * 36; i += 128) {
-                const int r = i / 36, c = i - r * 36;
-                const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
-                                     (long long)(b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
-                *reinterpret_cast<uint4*>(smem + L::OFF_Q + (c >> 3) * (N * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-            }
-            fence_proxy_async();
-            mbar_arrive(&ms.q_full);
-            if (tid == 0) TRACE(2, 63);
+            Walker wk; wk.init(prefix, p.batch, t_begin);
             // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key
             float nm[N], l_acc[N];
-#pragma unroll
-            for (int c = 0; c < N; ++c) { nm[c] = INFINITY; l_acc[c] = 0.0f; }
             // token position pos is visible to the rows of 16-column chunk q iff pos < lim[q]
             // (heads is a multiple of 16, so the query index j is constant inside a chunk)
-            int lim[N / 16], lim_min = 0x7fffffff;
-#pragma unroll
-            for (int q = 0; q < N / 16; ++q) {
-                const int j = (row0 + 16 * q) / p.heads;
-                const int causal_lim = p.causal ? (tot_len - p.q_len + j + 1 - pos_off) : 0x7fffffff;
-                lim[q] = min(seq_len, causal_lim);
-                lim_min = min(lim_min, lim[q]);
-            }
+            int lim[N / 16], lim_min = 0;
             // per-column reduction over the 128 threads; result replicated in every thread
             auto reduce_cols = [&](float (&v)[N], bool is_max) {
 #pragma unroll
@@ -442,10 +471,25 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 }
                 named_bar_sync(1, 128);
             };
-            for (int i = 0; i < n_tiles; ++i) {
-                const int g = g0 + i, sb = g & 1;
+            for (int g = 0; g < n_total; ++g) {
+                const int sb = g & 1;
+                const bool first = wk.seek(p, prefix, t_begin + g);
+                const bool last = t_begin + g + 1 == min(t_end, wk.seq_t1);
+                const int pos_first = (t_begin + g - wk.seq_t0) * TILE;
+                if (first) {
+#pragma unroll
+                    for (int c = 0; c < N; ++c) { nm[c] = INFINITY; l_acc[c] = 0.0f; }
+                    lim_min = 0x7fffffff;
+#pragma unroll
+                    for (int q = 0; q < N / 16; ++q) {
+                        const int j = (row0 + 16 * q) / p.heads;
+                        const int causal_lim = p.causal ? (wk.tot_len - p.q_len + j + 1 - wk.pos_off) : 0x7fffffff;
+                        lim[q] = min(wk.seq_len, causal_lim);
+                        lim_min = min(lim_min, lim[q]);
+                    }
+                }
                 mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
-                if (tid == 0) TRACE(6, 2 * g);
+                if (tid == 0) TRACE(6, g);
                 tc_fence_after();
                 float s[N];
 #pragma unroll
@@ -455,8 +499,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 mbar_arrive(&ms.s_empty[sb]);
 
                 // x = log2-domain exponent of the stored probability: score*scale - m_ref + P_SCALE_LOG2
-                const int pos = pos_first + i * TILE + tok;
-                const bool masked_tile = pos_first + (i + 1) * TILE > lim_min;       // uniform
+                const int pos = pos_first + tid;
+                const bool masked_tile = pos_first + TILE > lim_min;                 // uniform
                 float x[N];
 #pragma unroll
                 for (int c = 0; c < N; ++c) x[c] = fmaf(s[c], score_scale, nm[c]);
@@ -467,9 +511,9 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 float xm = x[0];
 #pragma unroll
                 for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
-                if (tid == 0) TRACE(7, 2 * g);
+                if (tid == 0) TRACE(7, g);
                 const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
-                if (tid == 0) TRACE(8, 2 * g);
+                if (tid == 0) TRACE(8, g);
                 if (recenter) {
                     float mx[N];
 #pragma unroll
@@ -487,8 +531,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         l_acc[c] *= f[c];
                         x[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : fmaf(s[c], score_scale, nm[c]);
                     }
-                    if (i > 0 && any) {
-                        // O holds tiles 0..i-1 once PV(g-1) has completed; nothing else touches it until P(g) is published
+                    if (!first && any) {
+                        // O holds the sequence's earlier tiles once PV(g-1) has completed; nothing else touches it until P(g) is published
                         mbar_wait(&ms.p_empty[(g - 1) & 1], (g - 1) / 2, abort_flag);
                         tc_fence_after();
 #pragma unroll
@@ -510,7 +554,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 }
                 // P(g) may overwrite its buffer once PV(g-2) has completed
                 mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
-                if (tid == 0) TRACE(9, 2 * g);
+                if (tid == 0) TRACE(9, g);
                 uint8_t* pbuf = smem + L::OFF_P + sb * L::P_BUF_BYTES;
 #pragma unroll
                 for (int c0 = 0; c0 < N; c0 += 16) {
@@ -529,67 +573,65 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         lo[q4] = pack_e4m3x4((pv[0] - h01.x) * 16.0f, (pv[1] - h01.y) * 16.0f,
                                              (pv[2] - h23.x) * 16.0f, (pv[3] - h23.y) * 16.0f);
                     }
-                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (TILE * 16) + tok * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (TILE * 16) + tok * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (TILE * 16) + tid * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (TILE * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
                 fence_proxy_async();
                 mbar_arrive(&ms.p_full[sb]);
-                if (tid == 0) TRACE(10, 2 * g);
-            }
-            // ---- epilogue of this (CTA, sequence) pair
-            {
-                const int gl = g0 + n_tiles - 1;
-                mbar_wait(&ms.p_empty[gl & 1], gl / 2, abort_flag);
-                if (tid == 0) TRACE(3, 63);
-                tc_fence_after();
-                reduce_cols(l_acc, false);
-                const bool whole = (t == seq_t0) && (my_t1 == seq_t1);
-                const int slot = w + b;
-                float inv[N];
+                if (tid == 0) TRACE(10, g);
+
+                if (last) {
+                    // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
+                    mbar_wait(&ms.p_empty[sb], g / 2, abort_flag);
+                    if (tid == 0) TRACE(3, 63);
+                    tc_fence_after();
+                    reduce_cols(l_acc, false);
+                    const bool whole = (t_begin <= wk.seq_t0) && (wk.seq_t1 <= t_end);
+                    const int slot = w + wk.b;
+                    float inv[N];
 #pragma unroll
-                for (int c = 0; c < N; ++c) inv[c] = l_acc[c] > 0.0f ? __fdividef(out_scale, l_acc[c]) : 0.0f;
-                // one output element per (row, dim): this thread owns dims tid, 128+tid, ... of every row
-                const long long orow0 = whole ? ((long long)b * p.rows + row0) : ((long long)slot * p.rows + row0);
-                float* dst_f32 = whole ? p.out_o_f32 : p.part_o;
-                __nv_bfloat16* dst_bf16 = whole ? p.out : nullptr;
-                if (dst_f32) dst_f32 += orow0 * V_DIM + tid;
-                if (dst_bf16) dst_bf16 += orow0 * V_DIM + tid;
+                    for (int c = 0; c < N; ++c) inv[c] = l_acc[c] > 0.0f ? __fdividef(out_scale, l_acc[c]) : 0.0f;
+                    // one output element per (row, dim): this thread owns dims tid, 128+tid, ... of every row
+                    const long long orow0 = whole ? ((long long)wk.b * p.rows + row0) : ((long long)slot * p.rows + row0);
+                    float* dst_f32 = whole ? p.out_o_f32 : p.part_o;
+                    __nv_bfloat16* dst_bf16 = whole ? p.out : nullptr;
+                    if (dst_f32) dst_f32 += orow0 * V_DIM + tid;
+                    if (dst_bf16) dst_bf16 += orow0 * V_DIM + tid;
 #pragma unroll
-                for (int jb = 0; jb < 4; ++jb) {
+                    for (int jb = 0; jb < 4; ++jb) {
 #pragma unroll
-                    for (int c0 = 0; c0 < N; c0 += 16) {
-                        float ohi[16], olo[16];
-                        tmem_ld16(tmem + lane_base + L::TMEM_O + jb * 2 * N + c0, ohi);
-                        tmem_ld16(tmem + lane_base + L::TMEM_O + jb * 2 * N + N + c0, olo);
-                        tmem_wait_ld();
+                        for (int c0 = 0; c0 < N; c0 += 16) {
+                            float ohi[16], olo[16];
+                            tmem_ld16(tmem + lane_base + L::TMEM_O + jb * 2 * N + c0, ohi);
+                            tmem_ld16(tmem + lane_base + L::TMEM_O + jb * 2 * N + N + c0, olo);
+                            tmem_wait_ld();
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) ohi[c] = fmaf(olo[c], 0.0625f, ohi[c]) * inv[c0 + c];
-                        if (dst_bf16) {
+                            for (int c = 0; c < 16; ++c) ohi[c] = fmaf(olo[c], 0.0625f, ohi[c]) * inv[c0 + c];
+                            if (dst_bf16) {
 #pragma unroll
-                            for (int c = 0; c < 16; ++c) dst_bf16[(c0 + c) * V_DIM + jb * 128] = __float2bfloat16_rn(ohi[c]);
-                        }
-                        if (dst_f32) {
+                                for (int c = 0; c < 16; ++c) dst_bf16[(c0 + c) * V_DIM + jb * 128] = __float2bfloat16_rn(ohi[c]);
+                            }
+                            if (dst_f32) {
 #pragma unroll
-                            for (int c = 0; c < 16; ++c) dst_f32[(c0 + c) * V_DIM + jb * 128] = ohi[c];
+                                for (int c = 0; c < 16; ++c) dst_f32[(c0 + c) * V_DIM + jb * 128] = ohi[c];
+                            }
                         }
                     }
-                }
-                if (tid < N) {
-                    float lsum = 0.0f, nmc = 0.0f;
+                    // O has been read: the next sequence's first PV may overwrite it
+                    tc_fence_before();
+                    mbar_arrive(&ms.o_free);
+                    if (tid < N) {
+                        float lsum = 0.0f, nmc = 0.0f;
 #pragma unroll
-                    for (int c = 0; c < N; ++c) if (c == tid) { lsum = l_acc[c]; nmc = nm[c]; }
-                    const float lse = lsum > 0.0f ? (log2f(lsum) - nmc) * LN2 : -INFINITY;
-                    if (whole) { if (p.out_lse) p.out_lse[(long long)b * p.rows + row0 + tid] = lse; }
-                    else p.part_lse[(long long)slot * p.rows + row0 + tid] = lse;
+                        for (int c = 0; c < N; ++c) if (c == tid) { lsum = l_acc[c]; nmc = nm[c]; }
+                        const float lse = lsum > 0.0f ? (log2f(lsum) - nmc) * LN2 : -INFINITY;
+                        if (whole) { if (p.out_lse) p.out_lse[(long long)wk.b * p.rows + row0 + tid] = lse; }
+                        else p.part_lse[(long long)slot * p.rows + row0 + tid] = lse;
+                    }
+                    if (tid == 0) TRACE(4, 63);
                 }
-                tc_fence_before();
             }
         }
-        g0 += n_tiles;
-        ++pair_idx;
-        t = my_t1;
-        __syncthreads();              // pair boundary: every role is drained
-        if (tid == 0) TRACE(4, 63);
     }
 
     __syncthreads();
@@ -601,7 +643,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
 }  // namespace sm100
 
 bool sm100_supported(const MlaParams& p) {
-    return p.kv_format == KV_E4M3 && p.q_format == Q_E4M3 && p.rows % 16 == 0;
+    // the tile-prefix table shares the tail of shared memory with the rings: batch <= 4096
+    return p.kv_format == KV_E4M3 && p.q_format == Q_E4M3 && p.rows % 16 == 0 && p.batch <= 4096;
 }
 int sm100_rows_per_cta(const MlaParams& p) { return p.rows % 32 == 0 ? 32 : 16; }
 

@@ -157,14 +157,16 @@ def test_pages_larger_than_one_token(pkg, impl):
     page_ids = torch.randperm(npages, generator=g)[: sum(pages_per)].to(torch.int32)
     page_indptr = torch.tensor([0] + list(np.cumsum(pages_per)), dtype=torch.int32)
     kv_indptr = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
-    out = pkg.mla_decode(q, None, "fp8", kvd["fp8"], kv_indptr.cuda(), sm_scale=cfg["sm_scale"],
+    q8, q8_scale = pkg.quantize_q_fp8(q)
+    out = pkg.mla_decode(q8, q8_scale, "fp8", kvd["fp8"], kv_indptr.cuda(), sm_scale=cfg["sm_scale"],
                          kv_indices=page_ids.cuda(), page_size=page, kv_page_indptr=page_indptr.cuda(), impl=impl)
     # oracle: expand the page table to token slots
     slots = []
     for b, n in enumerate(lens):
         for t in range(n):
             slots.append(int(page_ids[page_indptr[b] + t // page]) * page + t % page)
-    ref = mo.decode_from_data(q.cpu(), None, "fp8", tuple(t.cpu() for t in kvd["fp8"]), kv_indptr.numpy(),
+    qc, qs = mo.quantize_fp8_per_tensor(q.cpu())
+    ref = mo.decode_from_data(qc, qs, "fp8", tuple(t.cpu() for t in kvd["fp8"]), kv_indptr.numpy(),
                               np.array(slots, np.int32), cfg["sm_scale"])
     assert_close(out, ref, tight=1.5e-2)
 
