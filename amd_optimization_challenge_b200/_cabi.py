@@ -52,7 +52,7 @@ def _load() -> ctypes.CDLL:
     lib.b200_mla_decode.restype = _i32
     lib.b200_mla_decode.argtypes = [ctypes.POINTER(DecodeArgs), _vp]
     lib.b200_mla_combine.restype = _i32
-    lib.b200_mla_combine.argtypes = [_vp, _vp, _i32, _i64, _vp, _vp, _vp]
+    lib.b200_mla_combine.argtypes = [_vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp]
     lib.b200_mla_quantize_fp8.restype = _i32
     lib.b200_mla_quantize_fp8.argtypes = [_vp, _i64, _vp, _vp, _vp, _vp]
     lib.b200_mla_set_stage1_events.restype = _i32

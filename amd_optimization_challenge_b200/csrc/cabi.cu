@@ -15,7 +15,8 @@ bool sm100_supported(const MlaParams& p);
 int sm100_rows_per_cta(const MlaParams& p);
 cudaError_t launch_combine_spans(const MlaParams& p, cudaStream_t stream);
 cudaError_t launch_combine_parts(const float* o_parts, const float* lse_parts, int parts, long long rows,
-                                 __nv_bfloat16* out, float* out_lse, cudaStream_t stream);
+                                 long long o_stride, long long lse_stride, __nv_bfloat16* out, float* out_lse,
+                                 cudaStream_t stream);
 cudaError_t launch_quantize_fp8(const __nv_bfloat16* x, long long n, uint8_t* out, float* scale_out,
                                 unsigned int* scratch, cudaStream_t stream);
 }  // namespace b200mla
@@ -170,13 +171,18 @@ int32_t b200_mla_set_stage1_events(void* start_event, void* stop_event) {
     return B200_MLA_OK;
 }
 
-int32_t b200_mla_combine(const float* o_parts, const float* lse_parts, int32_t parts, int64_t rows, void* out,
-                         float* out_lse, void* stream) {
+int32_t b200_mla_combine(const float* o_parts, const float* lse_parts, int32_t parts, int64_t rows,
+                         int64_t o_part_stride, int64_t lse_part_stride, void* out, float* out_lse, void* stream) {
     if (!o_parts || !lse_parts || !out) return fail(B200_MLA_ERR_INVALID_ARG, "o_parts, lse_parts and out are required");
     if (parts <= 0 || rows <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "parts and rows must be positive");
     if (rows > 0x7fffffffLL) return fail(B200_MLA_ERR_TOO_LARGE, "rows exceeds 2^31-1");
     if (((uintptr_t)o_parts & 15) || ((uintptr_t)out & 7)) return fail(B200_MLA_ERR_INVALID_ARG, "o_parts must be 16-byte and out 8-byte aligned");
-    cudaError_t e = launch_combine_parts(o_parts, lse_parts, parts, rows, (__nv_bfloat16*)out, out_lse, (cudaStream_t)stream);
+    if (o_part_stride == 0) o_part_stride = rows * V_DIM;
+    if (lse_part_stride == 0) lse_part_stride = rows;
+    if (o_part_stride < rows * V_DIM || lse_part_stride < rows || (o_part_stride & 3))
+        return fail(B200_MLA_ERR_INVALID_ARG, "part strides must cover a part; the O stride must be a multiple of 4 elements");
+    cudaError_t e = launch_combine_parts(o_parts, lse_parts, parts, rows, o_part_stride, lse_part_stride,
+                                        (__nv_bfloat16*)out, out_lse, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(e));
     return B200_MLA_OK;
 }

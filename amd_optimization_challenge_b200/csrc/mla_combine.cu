@@ -60,17 +60,18 @@ __global__ void __launch_bounds__(128) combine_spans_kernel(const MlaParams p) {
 
 __global__ void __launch_bounds__(128) combine_parts_kernel(const float* __restrict__ o_parts,
                                                             const float* __restrict__ lse_parts, int parts,
-                                                            long long rows, __nv_bfloat16* out, float* out_lse) {
+                                                            long long rows, long long o_stride, long long lse_stride,
+                                                            __nv_bfloat16* out, float* out_lse) {
     const long long r = blockIdx.x;
     const int d = threadIdx.x * 4;
     float M = -INFINITY;
-    for (int i = 0; i < parts; ++i) M = fmaxf(M, lse_parts[i * rows + r]);
+    for (int i = 0; i < parts; ++i) M = fmaxf(M, lse_parts[i * lse_stride + r]);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float den = 0.f;
     if (M > -INFINITY) {
         for (int i = 0; i < parts; ++i) {
-            const float wt = expf(lse_parts[i * rows + r] - M);
-            const float4 v = *reinterpret_cast<const float4*>(o_parts + (i * rows + r) * V_DIM + d);
+            const float wt = expf(lse_parts[i * lse_stride + r] - M);
+            const float4 v = *reinterpret_cast<const float4*>(o_parts + i * o_stride + r * V_DIM + d);
             acc.x += wt * v.x; acc.y += wt * v.y; acc.z += wt * v.z; acc.w += wt * v.w;
             den += wt;
         }
@@ -90,8 +91,9 @@ cudaError_t launch_combine_spans(const MlaParams& p, cudaStream_t stream) {
 }
 
 cudaError_t launch_combine_parts(const float* o_parts, const float* lse_parts, int parts, long long rows,
-                                 __nv_bfloat16* out, float* out_lse, cudaStream_t stream) {
-    combine_parts_kernel<<<(unsigned)rows, 128, 0, stream>>>(o_parts, lse_parts, parts, rows, out, out_lse);
+                                 long long o_stride, long long lse_stride, __nv_bfloat16* out, float* out_lse,
+                                 cudaStream_t stream) {
+    combine_parts_kernel<<<(unsigned)rows, 128, 0, stream>>>(o_parts, lse_parts, parts, rows, o_stride, lse_stride, out, out_lse);
     return cudaGetLastError();
 }
 

@@ -1,0 +1,152 @@
+"""Multi-GPU decode: one process per GPU, `torch.distributed` for the plumbing.
+
+The reference is single-GPU only (no collective call exists anywhere in it); the two modes below
+are the ones the decode path shards into naturally.
+
+* Batch sharding (no collective).  Sequences are independent - each touches only its own
+  kv_indptr range (mixed-mla/submission.py:154-160) - so ragged batches are split over the ranks
+  by a token-balanced partition and every rank runs the ordinary `custom_kernel` on its shard.
+* Split-KV across GPUs (one all-gather).  Rank r holds the keys [r*S/n, (r+1)*S/n) of every
+  sequence, decodes them into a normalised fp32 partial O and its log-sum-exp, all ranks exchange
+  the fused (O || LSE) buffer with ONE all-gather over NVLink, and the LSE-combine kernel merges
+  the n partials (the merge of mixed-mla/submission.py:257-294, across GPUs instead of splits).
+
+The compute callables are injectable so that the sharding / gather / merge logic is covered by
+CPU tests with the `gloo` backend; the defaults are the CUDA kernels.
+"""
+from __future__ import annotations
+
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+V_DIM = 512
+
+
+# --------------------------------------------------------------------------------------------
+# partitions (host logic, no device work)
+# --------------------------------------------------------------------------------------------
+
+def token_balanced_partition(kv_lens: Sequence[int], world: int) -> list[list[int]]:
+    """Assign sequences to `world` ranks so that the token counts are balanced: longest first,
+    each to the currently lightest rank (LPT).  Returns, per rank, the sequence ids in ascending
+    order.  Deterministic; every rank computes the same answer."""
+    if world < 1:
+        raise ValueError("world must be >= 1")
+    order = sorted(range(len(kv_lens)), key=lambda i: (-int(kv_lens[i]), i))
+    load = [0] * world
+    out: list[list[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda k: (load[k], k))
+        out[r].append(i)
+        load[r] += int(kv_lens[i])
+    return [sorted(s) for s in out]
+
+
+def kv_range_partition(seq_len: int, world: int, granule: int = 128) -> list[tuple[int, int]]:
+    """Contiguous key ranges [begin, end) per rank for the cross-GPU split-KV mode, boundaries
+    rounded to `granule` tokens (the kernels' tile) so that no tile straddles two GPUs."""
+    if world < 1:
+        raise ValueError("world must be >= 1")
+    per = -(-seq_len // world)
+    per = -(-per // granule) * granule
+    return [(min(r * per, seq_len), min((r + 1) * per, seq_len)) for r in range(world)]
+
+
+def shard_batch(data, seq_ids: Sequence[int]):
+    """The sub-problem made of the sequences `seq_ids` of a (q, kv_data, qo_indptr, kv_indptr,
+    config) tuple: q rows, indptrs and the page table are re-based; the cache planes are shared
+    (a rank of a real deployment would hold only its own pages).  Host-side helper used by the
+    tests and by callers that start from a global batch; needs `config["kv_indices"]`."""
+    q, kv_data, qo_indptr, kv_indptr, config = data
+    ql = int(config.get("q_seq_len", 1))
+    ip = kv_indptr.cpu().tolist()
+    idx = config["kv_indices"]
+    rows = torch.cat([torch.arange(b * ql, (b + 1) * ql) for b in seq_ids]) if seq_ids else torch.zeros(0, dtype=torch.long)
+    lens = [ip[b + 1] - ip[b] for b in seq_ids]
+    new_idx = torch.cat([idx[ip[b]:ip[b + 1]] for b in seq_ids]) if seq_ids else idx[:0]
+    new_ip = torch.zeros(len(seq_ids) + 1, dtype=torch.int32)
+    if lens:
+        new_ip[1:] = torch.cumsum(torch.tensor(lens, dtype=torch.int64), 0).to(torch.int32)
+    cfg = dict(config)
+    cfg.update(batch_size=len(seq_ids), kv_indices=new_idx.contiguous(), total_kv=int(sum(lens)), kv_lens=lens)
+    new_qo = (torch.arange(len(seq_ids) + 1, dtype=torch.int32) * ql).to(qo_indptr.device)
+    return (q[rows.to(q.device)].contiguous(), kv_data, new_qo, new_ip.to(kv_indptr.device), cfg)
+
+
+# --------------------------------------------------------------------------------------------
+# batch sharding: no data-path collective
+# --------------------------------------------------------------------------------------------
+
+def decode_batch_sharded(local_data, decode_fn: Callable | None = None):
+    """Decode this rank's shard of a batch.  There is nothing to exchange: the result rows belong
+    to this rank's sequences only.  Exists so that both multi-GPU modes have the same shape of
+    call; `decode_fn` defaults to `custom_kernel`."""
+    if decode_fn is None:
+        from .submission import custom_kernel as decode_fn
+    return decode_fn(local_data)
+
+
+# --------------------------------------------------------------------------------------------
+# split-KV across GPUs: local partial -> one all-gather -> LSE combine
+# --------------------------------------------------------------------------------------------
+
+class SplitKVDecoder:
+    """Holds the persistent exchange buffers of the cross-GPU split-KV mode for one problem shape.
+
+    rows = batch * q_len query rows, `heads` heads.  The local partial lives in `send`
+    (rows*heads*512 floats of O followed by rows*heads floats of LSE) and is written in place by
+    the stage-1 / combine kernels; `recv` holds the world's partials after the all-gather and is
+    read in place by the merge.  Nothing is copied between the kernels and the collective.
+    """
+
+    def __init__(self, rows: int, heads: int, device, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.rows, self.heads = rows, heads
+        self.n_o = rows * heads * V_DIM
+        self.n = self.n_o + rows * heads
+        self.send = torch.empty(self.n, dtype=torch.float32, device=device)
+        self.recv = torch.empty(self.world * self.n, dtype=torch.float32, device=device)
+
+    # views into the fused buffers ---------------------------------------------------------
+    def local_o(self) -> torch.Tensor:
+        return self.send[: self.n_o].view(self.rows, self.heads, V_DIM)
+
+    def local_lse(self) -> torch.Tensor:
+        return self.send[self.n_o:].view(self.rows, self.heads)
+
+    def gathered(self):
+        g = self.recv.view(self.world, self.n)
+        return (g[:, : self.n_o].unflatten(1, (self.rows, self.heads, V_DIM)),
+                g[:, self.n_o:].unflatten(1, (self.rows, self.heads)))
+
+    # one decode step ------------------------------------------------------------------------
+    def step(self, partial_fn: Callable, merge_fn: Callable | None = None):
+        """partial_fn(out_o, out_lse) must fill this rank's normalised partial O and LSE (views
+        of the send buffer); returns the merged bf16 O [rows, heads, 512] on every rank."""
+        partial_fn(self.local_o(), self.local_lse())
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+        else:
+            self.recv.copy_(self.send)
+        o_parts, lse_parts = self.gathered()
+        if merge_fn is None:
+            from .submission import combine_partials_strided
+            return combine_partials_strided(self.recv, self.world, self.n, self.n_o, self.rows, self.heads)
+        return merge_fn(o_parts, lse_parts)
+
+
+def cuda_partial_fn(q, q_scale, kv_format: str, kv_local, kv_indptr_local, *, sm_scale: float, q_len: int,
+                    kv_indices=None, kv_pos_offset=None, kv_total_len=None, total_kv_hint: int = 0, impl: str = "auto"):
+    """The default producer of a rank's partial for SplitKVDecoder.step: the CUDA decode writing
+    its normalised fp32 O and LSE straight into the send buffer."""
+    from .submission import mla_decode
+
+    def fn(out_o, out_lse):
+        mla_decode(q, q_scale, kv_format, kv_local, kv_indptr_local, sm_scale=sm_scale, q_len=q_len,
+                   kv_indices=kv_indices, kv_pos_offset=kv_pos_offset, kv_total_len=kv_total_len,
+                   total_kv_hint=total_kv_hint, return_partial=True, partial_out=(out_o, out_lse), impl=impl)
+    return fn

@@ -84,7 +84,7 @@ def quantize_q_fp8(q: torch.Tensor):
 def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Tensor, *, sm_scale: float,
                q_len: int = 1, kv_indices=None, page_size: int = 1, kv_page_indptr=None, causal: bool = True,
                total_kv_hint: int = 0, kv_pos_offset=None, kv_total_len=None, return_partial: bool = False,
-               impl: str = "auto", max_ctas: int = 0):
+               impl: str = "auto", max_ctas: int = 0, partial_out=None):
     """One decode call through b200_mla_decode.
 
     q         [batch*q_len, heads, 576] bf16, or float8_e4m3fn/uint8 codes with `q_scale` (f32[1])
@@ -150,8 +150,13 @@ def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Te
     a.kv_pos_offset, a.kv_total_len = _ptr(kv_pos_offset), _ptr(kv_total_len)
 
     if return_partial:
-        o32 = torch.empty(rows_total, heads, V_DIM, dtype=torch.float32, device=dev)
-        lse = torch.empty(rows_total, heads, dtype=torch.float32, device=dev)
+        if partial_out is not None:                   # caller-owned (e.g. the all-gather send buffer)
+            o32, lse = partial_out
+            if not (o32.is_contiguous() and lse.is_contiguous() and o32.dtype == torch.float32 and lse.dtype == torch.float32):
+                raise ValueError("partial_out must be contiguous fp32 tensors")
+        else:
+            o32 = torch.empty(rows_total, heads, V_DIM, dtype=torch.float32, device=dev)
+            lse = torch.empty(rows_total, heads, dtype=torch.float32, device=dev)
         a.out_o_f32, a.out_lse = o32.data_ptr(), lse.data_ptr()
         result = (o32, lse)
     else:
@@ -176,9 +181,21 @@ def combine_partials(o_parts: torch.Tensor, lse_parts: torch.Tensor, return_lse:
     out = torch.empty(out_shape, dtype=torch.bfloat16, device=o_parts.device)
     lse = torch.empty(out_shape[:-1], dtype=torch.float32, device=o_parts.device) if return_lse else None
     with torch.cuda.device(o_parts.device):
-        check(lib.b200_mla_combine(o_parts.data_ptr(), lse_parts.data_ptr(), parts, rows, out.data_ptr(),
+        check(lib.b200_mla_combine(o_parts.data_ptr(), lse_parts.data_ptr(), parts, rows, 0, 0, out.data_ptr(),
                                    _ptr(lse), _stream(o_parts.device)), "b200_mla_combine")
     return (out, lse) if return_lse else out
+
+
+def combine_partials_strided(buf: torch.Tensor, parts: int, part_stride: int, lse_offset: int, rows: int, heads: int):
+    """Merge `parts` fused (O || LSE) fp32 records laid out back to back in `buf` (the receive
+    buffer of an all-gather) without copying: record i starts at i*part_stride, its LSE block at
+    +lse_offset.  Returns bf16 [rows, heads, 512]."""
+    out = torch.empty(rows, heads, V_DIM, dtype=torch.bfloat16, device=buf.device)
+    base = buf.data_ptr()
+    with torch.cuda.device(buf.device):
+        check(lib.b200_mla_combine(base, base + 4 * lse_offset, parts, rows * heads, part_stride, part_stride,
+                                   out.data_ptr(), None, _stream(buf.device)), "b200_mla_combine")
+    return out
 
 
 def custom_kernel(data):

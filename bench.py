@@ -49,6 +49,9 @@ WORKLOADS = {
                desc="bf16 Q + MXFP4 KV, B8 H16 q2 S131072 causal (BASELINE configs[4])"),
 }
 KV_ROW_BYTES = {"fp8": 576, "mxfp4": 306, "hybrid": 336}
+# how a workload uses N > 1 GPUs: independent replicas (weak scaling), a token-balanced split of the
+# batch (strong, no collective), or each sequence's keys split over the GPUs (strong, one all-gather)
+MODES = {"c1": "replica", "c2": "replica", "c3": "batch_shard", "c4": "split_kv"}
 L2_BYTES = 126 << 20
 
 
@@ -167,14 +170,33 @@ def main():
 
     import amd_optimization_challenge_b200.inputs as gen   # plain torch
 
-    def build_host(seed):
-        lens = make_lens(w, seed)
-        data = gen.generate_input(w["batch"], w["q_len"], w["kv_len"] if lens is None else max(lens), seed,
+    mode = MODES[args.workload] if world > 1 else "replica"
+
+    def build_host(seed, shard_rank=0, shard_world=1, shard_mode="replica"):
+        """Seeded host-side inputs of one rank: the whole workload, or this rank's shard of it."""
+        lens = make_lens(w, 1234)                                 # the same ragged lengths on every rank
+        batch, kv_len, extra = w["batch"], w["kv_len"], {}
+        if shard_mode == "batch_shard":
+            from amd_optimization_challenge_b200.distributed import token_balanced_partition
+            all_lens = lens if lens is not None else [kv_len] * batch
+            ids = token_balanced_partition(all_lens, shard_world)[shard_rank]
+            lens, batch = [all_lens[i] for i in ids], len(ids)
+            extra["global_total_kv"] = sum(all_lens)
+        elif shard_mode == "split_kv":
+            from amd_optimization_challenge_b200.distributed import kv_range_partition
+            a, b = kv_range_partition(kv_len, shard_world)[shard_rank]
+            extra.update(kv_pos_offset=a, kv_total_len=kv_len, global_total_kv=batch * kv_len)
+            kv_len = b - a
+        data = gen.generate_input(batch, w["q_len"], kv_len if lens is None else max(lens), seed,
                                   num_heads=w["heads"], kv_lens=lens, shuffle_pages=True,
                                   formats=(w["kv_format"],), device="cpu")
         q, kvd, qo, kvp, cfg = data
-        return dict(w=w, q=q, kv=kvd[w["kv_format"]], qo=qo, kv_indptr=kvp, kv_indices=cfg["kv_indices"],
-                    sm_scale=cfg["sm_scale"], cfg=cfg, total_kv=cfg["total_kv"])
+        if shard_mode == "split_kv":                              # Q is replicated: draw it from a rank-independent seed
+            q = gen.generate_input(batch, w["q_len"], 1, 4321, num_heads=w["heads"], formats=(), device="cpu")[0]
+        h = dict(w=w, q=q, kv=kvd[w["kv_format"]], qo=qo, kv_indptr=kvp, kv_indices=cfg["kv_indices"],
+                 sm_scale=cfg["sm_scale"], cfg=cfg, total_kv=cfg["total_kv"], batch=batch)
+        h.update(extra)
+        return h
 
     # ------------------------------------------------------------------ reference arm (CPU)
     if args.impl == "reference":
@@ -215,8 +237,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     import amd_optimization_challenge_b200 as pkg
 
-    host = build_host(1234 + rank)
-    abytes = algorithmic_bytes(w, host["total_kv"])
+    host = build_host(1234 + rank, rank, world, mode)
+    w_rank = dict(w, batch=host["batch"])
+    abytes = algorithmic_bytes(w_rank, host["total_kv"])       # this rank's stage-1 launch
+    tokens_job = tokens_per_call if mode != "replica" else n_gpus * tokens_per_call
     kv_bytes = sum(t.numel() * t.element_size() for t in host["kv"])
     n_rot = max(2, -(-int(2.4 * L2_BYTES) // kv_bytes))         # rotate > 2.4x L2 worth of cache copies
     n_rot = min(n_rot, 6)
@@ -239,10 +263,29 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if mode == "split_kv":
+        from amd_optimization_challenge_b200.distributed import SplitKVDecoder, cuda_partial_fn
+        rows = host["batch"] * w["q_len"]
+        decoder = SplitKVDecoder(rows, w["heads"], dev)
+        d_off = torch.full((host["batch"],), host["kv_pos_offset"], dtype=torch.int32, device=dev)
+        d_tot = torch.full((host["batch"],), host["kv_total_len"], dtype=torch.int32, device=dev)
+
+        def call(data):
+            q, kvd, _, kvp, cfg = data
+            q_scale = None
+            if w["q_format"] == "fp8":
+                q, q_scale = pkg.quantize_q_fp8(q)
+            return decoder.step(cuda_partial_fn(q, q_scale, w["kv_format"], kvd[w["kv_format"]], kvp,
+                                                sm_scale=cfg["sm_scale"], q_len=w["q_len"], kv_indices=cfg["kv_indices"],
+                                                kv_pos_offset=d_off, kv_total_len=d_tot, total_kv_hint=host["total_kv"],
+                                                impl=args.kernel))
+    else:
+        call = pkg.custom_kernel
+
     # ---- launch vehicle: a CUDA graph holding n_rot consecutive steps (one per cache copy), so
     # that the timed region measures the GPU work and not the Python call overhead per step
     for i in range(max(args.warmup, 3)):
-        out = pkg.custom_kernel(rot[i % n_rot])
+        out = call(rot[i % n_rot])
     barrier()
     graph = None
     if not args.no_graph:
@@ -252,19 +295,19 @@ def main():
         with torch.cuda.stream(side):
             with torch.cuda.graph(graph, stream=side):
                 for i in range(n_rot):
-                    out = pkg.custom_kernel(rot[i])
+                    out = call(rot[i])
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
 
     def run_steps(k):
         if graph is None:
             for i in range(k):
-                pkg.custom_kernel(rot[i % n_rot])
+                call(rot[i % n_rot])
             return
         for _ in range(k // n_rot):
             graph.replay()
         for i in range(k % n_rot):
-            pkg.custom_kernel(rot[i])
+            call(rot[i])
 
     # ---- clocks are sampled from before the pre-roll (same work, untimed) to after the timed region
     sampler = ClockSampler(local_rank)
@@ -290,7 +333,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
-    value = n_gpus * tokens_per_call / (ms_per_step * 1e-3)
+    value = tokens_job / (ms_per_step * 1e-3)
 
     # ---- stage-1 kernel duration (CUDA events recorded by the library around that launch)
     lib = pkg._cabi.lib
@@ -305,7 +348,7 @@ def main():
     torch.cuda._sleep(int(2e7))                                  # ~10 ms of GPU spin: the calls below queue up behind
     for i, (a, b) in enumerate(pairs):                           # it, so no event waits on the host's launch latency
         lib.b200_mla_set_stage1_events(ctypes.c_void_p(a.cuda_event), ctypes.c_void_p(b.cuda_event))
-        out = pkg.custom_kernel(rot[i % n_rot])
+        out = call(rot[i % n_rot])
     lib.b200_mla_set_stage1_events(None, None)
     torch.cuda.synchronize()
     k_ms = [a.elapsed_time(b) for a, b in pairs]
@@ -332,7 +375,7 @@ def main():
         for d, h in zip(d_kv, h_kv):
             d.copy_(h, non_blocking=True)
         d_idx.copy_(h_idx, non_blocking=True); d_ip.copy_(h_ip, non_blocking=True); d_qo.copy_(h_qo, non_blocking=True)
-        o = pkg.custom_kernel((d_q, {w["kv_format"]: d_kv}, d_qo, d_ip, cfg_e))
+        o = call((d_q, {w["kv_format"]: d_kv}, d_qo, d_ip, cfg_e))
         h_out.copy_(o, non_blocking=True)
 
     e_steps = max(3, min(args.steps, 20))
@@ -349,7 +392,7 @@ def main():
         t = torch.tensor([e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e_ms = float(t.item())
-    e2e = {"value": n_gpus * tokens_per_call / (e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms,
+    e2e = {"value": tokens_job / (e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
     # ---- CPU baseline (rank 0, single-GPU runs only)
@@ -362,18 +405,25 @@ def main():
                "us_per_call": t_cpu * 1e6}
 
     launches_per_step = 2 + (2 if w["q_format"] == "fp8" else 0)     # [amax, cast,] stage 1, combine
+    if mode == "split_kv":
+        launches_per_step += 1                                        # merge of the gathered partials
+    per_gpu = {"replica": "each rank decodes its own batch, no collective",
+               "batch_shard": "token-balanced split of the batch over the ranks, no collective",
+               "split_kv": "each sequence's keys split over the ranks; (O || LSE) partials exchanged by one NCCL all-gather, then the LSE merge"}[mode]
     if rank == 0:
         line = {
             "metric": "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n_gpus,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "us_per_call": ms_per_step * 1e3, "achieved_gbs": abytes / (ms_per_step * 1e-3) / 1e9,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "us_per_call": ms_per_step * 1e3,
+            "achieved_gbs": (algorithmic_bytes(w, host.get("global_total_kv", host["total_kv"])) if mode != "replica"
+                             else n_gpus * abytes) / (ms_per_step * 1e-3) / 1e9,
+            "higher_is_better": True, "scaling": "weak" if mode == "replica" else "strong", "vs_baseline": None,
             "dtype": {"fp8": "e4m3", "mxfp4": "mxfp4(e2m1+e8m0)", "hybrid": "mxfp4+e4m3"}[w["kv_format"]] + " x f32 accumulate",
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: {w['desc']}", "kernel": args.kernel,
                        "launch": "eager custom_kernel calls" if graph is None else f"CUDA graph of {n_rot} custom_kernel steps, replayed",
                        "l2": f"rotating {n_rot} distinct copies of the {kv_bytes / 2**20:.1f} MiB cache (> 2x the 126 MB L2)",
-                       "per_gpu": "each rank decodes its own batch, no collective"},
+                       "per_gpu": per_gpu},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
             "gpu_launches": launches_per_step * args.steps,
         }

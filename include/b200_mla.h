@@ -132,14 +132,18 @@ int32_t b200_mla_decode(const b200_mla_decode_args *args, void *stream);
 /*
  * Log-sum-exp merge of `parts` normalised partial results, e.g. the per-GPU shards of a
  * split-KV sequence after an all-gather:
- *   o_parts  device fp32 [parts, rows, 512], lse_parts device fp32 [parts, rows]
- *   out      device bf16 [rows, 512];  out_lse optional device fp32 [rows]
+ *   o_parts   device fp32, part i at o_parts + i*o_part_stride, [rows, 512] dense inside a part
+ *   lse_parts device fp32, part i at lse_parts + i*lse_part_stride, [rows]
+ *   strides   in elements; 0 means dense ([parts, rows, 512] and [parts, rows]).  A fused
+ *             all-gather buffer holding (O || LSE) per rank is merged in place with
+ *             o_part_stride = lse_part_stride = rows*513 and lse_parts = o_parts + rows*512.
+ *   out       device bf16 [rows, 512];  out_lse optional device fp32 [rows]
  * Replaces _mla_mxfp4_reduce (mixed-mla/submission.py:257-294), aiter.mla_reduce_v1
  * (mixed-mla/asm_dumps/aiter_mla.py:421-430) and the (O, LSE) form of
  * competitor_submissions/dgavriloff_v114_hybrid_mxfp4k_fp8v.py:131-160.
  */
 int32_t b200_mla_combine(const float *o_parts, const float *lse_parts, int32_t parts, int64_t rows,
-                         void *out, float *out_lse, void *stream);
+                         int64_t o_part_stride, int64_t lse_part_stride, void *out, float *out_lse, void *stream);
 
 /*
  * Dynamic per-tensor e4m3fn quantisation of a dense bf16 tensor of n elements with the arithmetic

@@ -59,7 +59,7 @@ def test_argument_validation_without_gpu(built_lib):
     assert lib.b200_mla_decode(ctypes.byref(a), None) == -5
     a.batch = 1
     assert lib.b200_mla_decode(ctypes.byref(a), None) == -1          # null pointers
-    assert lib.b200_mla_combine(None, None, 1, 1, None, None, None) == -1
+    assert lib.b200_mla_combine(None, None, 1, 1, 0, 0, None, None, None) == -1
     assert lib.b200_mla_quantize_fp8(None, 8, None, None, None, None) == -1
     assert lib.b200_mla_workspace_bytes(0, 16, 1) == 0
     assert lib.b200_mla_workspace_bytes(32, 16, 1) > 32 * 16 * 512 * 4

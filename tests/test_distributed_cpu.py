@@ -1,0 +1,120 @@
+"""Host-side logic of the two multi-GPU modes, on CPU: partitions, shard construction and - with
+two `gloo` ranks - the all-gather + merge plumbing of the cross-GPU split-KV mode and the
+collective-free batch-sharded mode, with the CPU oracle standing in for the CUDA kernels."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import mla_oracle as mo
+from amd_optimization_challenge_b200 import distributed as D
+from amd_optimization_challenge_b200 import inputs
+
+
+def test_token_balanced_partition_properties():
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(1024, 16385, (128,), generator=g).tolist()
+    for world in (1, 2, 4, 8):
+        parts = D.token_balanced_partition(lens, world)
+        assert sorted(i for p in parts for i in p) == list(range(128))            # a partition
+        loads = [sum(lens[i] for i in p) for p in parts]
+        assert max(loads) - min(loads) <= max(lens)                                  # LPT bound
+        assert max(loads) <= 1.02 * sum(lens) / world + 1                            # near-even for this distribution
+        assert parts == D.token_balanced_partition(lens, world)                      # deterministic
+    assert D.token_balanced_partition([5, 0, 7], 4) == [[2], [0], [1], []]
+    with pytest.raises(ValueError):
+        D.token_balanced_partition([1], 0)
+
+
+def test_kv_range_partition():
+    for S, world in ((131072, 8), (131072, 2), (1000, 4), (100, 8), (0, 2)):
+        r = D.kv_range_partition(S, world)
+        assert r[0][0] == 0 and r[-1][1] == S and all(a[1] == b[0] for a, b in zip(r, r[1:]))
+        assert all(a % 128 == 0 for a, _ in r if a < S)
+    assert D.kv_range_partition(131072, 8)[3] == (49152, 65536)
+
+
+def test_shard_batch_matches_whole():
+    lens = [40, 0, 33, 70, 5]
+    data = inputs.generate_input(5, 2, 70, seed=3, kv_lens=lens, shuffle_pages=True, device="cpu", formats=("fp8",))
+    q, kvd, qo, kvp, cfg = data
+    whole = mo.decode_from_data(q, None, "fp8", kvd["fp8"], kvp.numpy(), cfg["kv_indices"].numpy(), cfg["sm_scale"], q_len=2)
+    parts = D.token_balanced_partition(lens, 2)
+    for ids in parts:
+        sq, skv, sqo, skp, scfg = D.shard_batch(data, ids)
+        assert sqo.tolist() == [2 * i for i in range(len(ids) + 1)] and scfg["batch_size"] == len(ids)
+        o = mo.decode_from_data(sq, None, "fp8", skv["fp8"], skp.numpy(), scfg["kv_indices"].numpy(), scfg["sm_scale"], q_len=2)
+        rows = torch.cat([torch.arange(2 * b, 2 * b + 2) for b in ids])
+        assert torch.equal(o, whole[rows])
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    return port
+
+
+def _split_kv_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, QL, H, S = 2, 2, 16, 300
+        data = inputs.generate_input(B, QL, S, seed=11, device="cpu", formats=("mxfp4",))   # same on every rank
+        q, kvd, _, kvp, cfg = data
+        kf = mo.dequant_kv("mxfp4", kvd["mxfp4"])
+        a, b = D.kv_range_partition(S, world)[rank]
+        n = b - a
+        idx = np.concatenate([np.arange(s * S + a, s * S + b) for s in range(B)]).astype(np.int32)
+        ip = np.arange(B + 1) * n
+
+        def partial_fn(out_o, out_lse):
+            o, l = mo.mla_decode(q.float(), kf, ip, idx, cfg["sm_scale"], q_len=QL, causal=True,
+                                 kv_pos_offset=[a] * B, kv_total_len=[S] * B)
+            out_o.copy_(o); out_lse.copy_(l)
+
+        dec = D.SplitKVDecoder(B * QL, H, "cpu")
+        merged = dec.step(partial_fn, merge_fn=lambda o, l: mo.merge_partials(o, l)[0])
+        whole, _ = mo.mla_decode(q.float(), kf, kvp.numpy(), None, cfg["sm_scale"], q_len=QL, causal=True)
+        ok = torch.allclose(merged, whole, atol=1e-5)
+        # the fused buffer really carries (O || LSE) of every rank
+        o_parts, lse_parts = dec.gathered()
+        ok = ok and o_parts.shape == (world, B * QL, H, 512) and lse_parts.shape == (world, B * QL, H)
+        ok = ok and torch.equal(o_parts[rank], dec.local_o()) and torch.equal(lse_parts[rank], dec.local_lse())
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def _batch_shard_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        lens = [90, 10, 64, 33, 0, 128]
+        data = inputs.generate_input(len(lens), 1, 128, seed=5, kv_lens=lens, shuffle_pages=True, device="cpu",
+                                     formats=("hybrid",))
+        ids = D.token_balanced_partition(lens, world)[rank]
+        shard = D.shard_batch(data, ids)
+        oracle = lambda d: mo.decode_from_data(d[0], None, "hybrid", d[1]["hybrid"], d[3].numpy(),
+                                               d[4]["kv_indices"].numpy(), d[4]["sm_scale"])
+        mine = D.decode_batch_sharded(shard, decode_fn=oracle)
+        whole = oracle(data)
+        ok = torch.equal(mine, whole[torch.tensor(ids, dtype=torch.long)]) if ids else mine.shape[0] == 0
+        # only bookkeeping crosses ranks: every sequence is owned exactly once
+        owned = [None] * world
+        dist.all_gather_object(owned, ids)
+        ok = ok and sorted(i for p in owned for i in p) == list(range(len(lens)))
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_split_kv_worker, _batch_shard_worker])
+def test_two_ranks_gloo(worker):
+    world = 2
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}

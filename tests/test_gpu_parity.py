@@ -297,3 +297,22 @@ def test_impls_agree_on_config1(pkg):
     a = _run(pkg, data, "fp8", "fp8", "generic")
     b = _run(pkg, data, "fp8", "fp8", "tcgen05")
     assert_close(a, b, rtol=1e-2, atol=1e-3)
+
+
+@pytest.mark.parametrize("impl", ["generic", "auto"])
+def test_split_kv_decoder_buffers_on_gpu(pkg, impl):
+    """The cross-GPU split-KV plumbing with a single rank: stage 1 writes its partial straight into
+    the fused (O || LSE) send buffer, the merge reads the gathered buffer in place."""
+    from amd_optimization_challenge_b200.distributed import SplitKVDecoder, cuda_partial_fn
+    B, QL, S = 3, 2, 700
+    data = pkg.generate_input(B, QL, S, seed=31, shuffle_pages=True, formats=("mxfp4",))
+    q, kvd, _, kvp, cfg = data
+    dec = SplitKVDecoder(B * QL, 16, q.device)
+    fn = cuda_partial_fn(q, None, "mxfp4", kvd["mxfp4"], kvp, sm_scale=cfg["sm_scale"], q_len=QL,
+                         kv_indices=cfg["kv_indices"], total_kv_hint=B * S, impl=impl)
+    merged = dec.step(fn)
+    torch.cuda.synchronize()
+    ref_o, ref_l = oracle_for_data(data, "mxfp4", "bf16", return_lse=True)
+    assert_close(merged, ref_o, tight=1.5e-2)
+    assert torch.allclose(dec.local_lse().cpu(), ref_l, atol=2e-2)
+    assert_close(dec.local_o(), ref_o, tight=1.5e-2)
