@@ -36,7 +36,7 @@ class DecodeArgs(ctypes.Structure):
 
 
 EXPORTS = ("b200_mla_version", "b200_mla_last_error", "b200_mla_workspace_bytes", "b200_mla_decode",
-           "b200_mla_combine", "b200_mla_quantize_fp8", "b200_mla_set_stage1_events")
+           "b200_mla_combine", "b200_mla_quantize_fp8", "b200_mla_set_stage1_events", "b200_mla_decode_static")
 
 
 def _load() -> ctypes.CDLL:
@@ -55,6 +55,8 @@ def _load() -> ctypes.CDLL:
     lib.b200_mla_combine.argtypes = [_vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp]
     lib.b200_mla_quantize_fp8.restype = _i32
     lib.b200_mla_quantize_fp8.argtypes = [_vp, _i64, _vp, _vp, _vp, _vp]
+    lib.b200_mla_decode_static.restype = _i32
+    lib.b200_mla_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), _vp]
     lib.b200_mla_set_stage1_events.restype = _i32
     lib.b200_mla_set_stage1_events.argtypes = [_vp, _vp]
     return lib

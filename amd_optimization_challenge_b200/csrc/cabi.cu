@@ -165,6 +165,43 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     return B200_MLA_OK;
 }
 
+}  // extern "C"
+
+// Scratch of the allocation-free entry point: lives in the library image, one copy per GPU.
+static __device__ __align__(256) unsigned char g_static_workspace[B200_MLA_STATIC_WORKSPACE_BYTES];
+
+extern "C" {
+
+int32_t b200_mla_decode_static(const b200_mla_decode_args* args, void* stream) {
+    if (!args) return fail(B200_MLA_ERR_INVALID_ARG, "args is NULL");
+    if (args->batch <= 0 || args->heads <= 0 || args->q_len <= 0)
+        return fail(B200_MLA_ERR_INVALID_ARG, "batch/heads/q_len must be positive");
+    const long long need = b200_mla_workspace_bytes(args->batch, args->heads, args->q_len);
+    if (need > (long long)B200_MLA_STATIC_WORKSPACE_BYTES)
+        return fail(B200_MLA_ERR_TOO_LARGE,
+                    "this problem needs %lld bytes of scratch, the built-in scratch of b200_mla_decode_static holds %u; "
+                    "use b200_mla_decode with a caller-provided workspace", need, (unsigned)B200_MLA_STATIC_WORKSPACE_BYTES);
+    // In host code the array's name is only a handle; its device address is looked up once per
+    // device, with that device current.
+    constexpr int kMaxDevices = 64;
+    static void* dev_ptr[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(B200_MLA_ERR_UNSUPPORTED, "device ordinal %d is beyond %d", dev, kMaxDevices);
+    void* ptr = __atomic_load_n(&dev_ptr[dev], __ATOMIC_ACQUIRE);
+    if (!ptr) {
+        e = cudaGetSymbolAddress(&ptr, g_static_workspace);
+        if (e != cudaSuccess || !ptr)
+            return fail(B200_MLA_ERR_CUDA, "cudaGetSymbolAddress(static workspace) failed: %s", cudaGetErrorString(e));
+        __atomic_store_n(&dev_ptr[dev], ptr, __ATOMIC_RELEASE);
+    }
+    b200_mla_decode_args a = *args;
+    a.workspace = ptr;
+    a.workspace_bytes = B200_MLA_STATIC_WORKSPACE_BYTES;
+    return b200_mla_decode(&a, stream);
+}
+
 int32_t b200_mla_set_stage1_events(void* start_event, void* stop_event) {
     g_ev_start = (cudaEvent_t)start_event;
     g_ev_stop = (cudaEvent_t)stop_event;

@@ -155,6 +155,28 @@ int32_t b200_mla_quantize_fp8(const void *x_bf16, int64_t n, void *codes_out, fl
                               void *scratch, void *stream);
 
 /*
+ * Decode without any allocation on the caller's side (no counterpart in the reference, whose
+ * wrappers allocate their partial buffers with torch on every path).
+ *
+ * For callers that cannot obtain device memory at call time: a serving loop whose memory pool is
+ * frozen after start-up, code running under a framework that forbids allocator calls in its hot
+ * section, or a plain C host that owns no allocator at all.  Same arguments and results as
+ * b200_mla_decode, except that `workspace` / `workspace_bytes` are ignored: the split-KV partials,
+ * the tile table and the status word live in a B200_MLA_STATIC_WORKSPACE_BYTES array that is part
+ * of the library image on every GPU that loads it (held until the process exits).
+ *   - A problem whose b200_mla_workspace_bytes() exceeds that size is refused with
+ *     B200_MLA_ERR_TOO_LARGE; nothing is launched.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - The call itself performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *   - All calls on a device share the one array: calls that overlap on the GPU (two streams, two
+ *     threads) race on the partials.  Contents persist from call to call; nothing in them has to
+ *     be cleared by the caller (the status word starts at zero and is sticky).
+ */
+#define B200_MLA_STATIC_WORKSPACE_BYTES (16u << 20)
+int32_t b200_mla_decode_static(const b200_mla_decode_args *args, void *stream);
+
+/*
  * Profiling aid (no counterpart in the reference, whose harness times whole calls, eval.py:225-261):
  * while both events (cudaEvent_t) are non-NULL, every b200_mla_decode issued by the calling thread
  * records `start` before and `stop` after its stage-1 kernel on the call's stream.  Pass NULLs to
