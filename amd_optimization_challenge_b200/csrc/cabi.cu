@@ -13,6 +13,11 @@ size_t generic_smem_bytes(int batch);
 cudaError_t launch_sm100(const MlaParams& p, int* status, cudaStream_t stream);
 bool sm100_supported(const MlaParams& p);
 int sm100_rows_per_cta(const MlaParams& p);
+cudaError_t launch_sm100x(const MlaParams& p, int* status, cudaStream_t stream);
+bool sm100x_supported(const MlaParams& p);
+int sm100x_rows_per_cta(const MlaParams& p);
+long long sm100x_q_split_bytes(int batch, int rows);
+long long sm100x_q_scale_bytes(int batch, int rows);
 cudaError_t launch_combine_spans(const MlaParams& p, cudaStream_t stream);
 cudaError_t launch_combine_parts(const float* o_parts, const float* lse_parts, int parts, long long rows,
                                  long long o_stride, long long lse_stride, __nv_bfloat16* out, float* out_lse,
@@ -52,15 +57,17 @@ int sm_count() {
 constexpr int kMaxCtasPerSm = 2;
 inline long long align256(long long x) { return (x + 255) & ~255LL; }
 
-// workspace: [status word | tile prefix | partial LSE | partial O]
-struct WsLayout { long long status_off, prefix_off, lse_off, o_off, total; };
+// workspace: [status word | tile prefix | split-Q scales | split-Q planes | partial LSE | partial O]
+struct WsLayout { long long status_off, prefix_off, qscale_off, qsplit_off, lse_off, o_off, total; };
 
 WsLayout ws_layout(int batch, int rows, int g_max) {
     WsLayout L;
     const long long slots = (long long)g_max + batch;
     L.status_off = 0;
     L.prefix_off = 256;
-    L.lse_off = L.prefix_off + align256((long long)(batch + 1) * 4);
+    L.qscale_off = L.prefix_off + align256((long long)(batch + 1) * 4);
+    L.qsplit_off = L.qscale_off + align256(sm100x_q_scale_bytes(batch, rows));
+    L.lse_off = L.qsplit_off + align256(sm100x_q_split_bytes(batch, rows));
     L.o_off = L.lse_off + align256(slots * rows * 4);
     L.total = L.o_off + align256(slots * rows * (long long)V_DIM * 4);
     return L;
@@ -124,18 +131,20 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     p.out = (__nv_bfloat16*)a->out; p.out_o_f32 = a->out_o_f32; p.out_lse = a->out_lse;
 
     const int sms = sm_count();
+    // two tcgen05 kernels: the plain one for e4m3 Q x e4m3 cache, the transforming one for every other pair
+    const bool plain = sm100_supported(p), xform = !plain && sm100x_supported(p);
     bool use_sm100 = false;
     if (a->impl == B200_MLA_IMPL_TCGEN05) {
-        if (!sm100_supported(p)) return fail(B200_MLA_ERR_UNSUPPORTED, "the tcgen05 kernel does not cover this shape / format");
+        if (!plain && !xform) return fail(B200_MLA_ERR_UNSUPPORTED, "the tcgen05 kernels do not cover this shape");
         use_sm100 = true;
     } else if (a->impl == B200_MLA_IMPL_AUTO) {
-        use_sm100 = sm100_supported(p);
+        use_sm100 = plain || xform;
     } else if (a->impl != B200_MLA_IMPL_GENERIC) {
         return fail(B200_MLA_ERR_INVALID_ARG, "bad impl %d", a->impl);
     }
 
     int ctas_per_sm;
-    if (use_sm100) { p.tile_tokens = 128; p.rows_per_cta = sm100_rows_per_cta(p); ctas_per_sm = 1; }
+    if (use_sm100) { p.tile_tokens = 128; p.rows_per_cta = plain ? sm100_rows_per_cta(p) : sm100x_rows_per_cta(p); ctas_per_sm = 1; }
     else { p.tile_tokens = 64; p.rows_per_cta = 16; ctas_per_sm = 2; }
     const int groups = p.rows / p.rows_per_cta;
     long long hint = a->total_kv_hint > 0 ? a->total_kv_hint : a->num_slots;
@@ -154,10 +163,14 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     p.tile_prefix = (int*)(ws + L.prefix_off);
     p.part_lse = (float*)(ws + L.lse_off);
     p.part_o = (float*)(ws + L.o_off);
+    p.q_split_scale = (float*)(ws + L.qscale_off);
+    p.q_split = (uint8_t*)(ws + L.qsplit_off);
 
     const bool prof = g_ev_start && g_ev_stop;
     if (prof) cudaEventRecord(g_ev_start, stream);
-    cudaError_t e = use_sm100 ? launch_sm100(p, (int*)(ws + L.status_off), stream) : launch_generic(p, stream);
+    cudaError_t e = !use_sm100 ? launch_generic(p, stream)
+                    : plain    ? launch_sm100(p, (int*)(ws + L.status_off), stream)
+                               : launch_sm100x(p, (int*)(ws + L.status_off), stream);
     if (prof) cudaEventRecord(g_ev_stop, stream);
     if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "stage-1 launch failed: %s", cudaGetErrorString(e));
     e = launch_combine_spans(p, stream);

@@ -35,21 +35,35 @@ __global__ void __launch_bounds__(128) combine_spans_kernel(const MlaParams p) {
     }
     const int w0 = cta_of_tile(t0, TT, G), w1 = cta_of_tile(t1 - 1, TT, G);
     if (w0 == w1) return;                                 // finished by a single stage-1 CTA
-    float M = -INFINITY;
-    // CTAs whose span is empty (G > total tiles) wrote nothing: skip them
-    for (int w = w0; w <= w1; ++w)
-        if (span_begin(w, TT, G) < span_begin(w + 1, TT, G)) M = fmaxf(M, p.part_lse[(long long)(w + b) * p.rows + r]);
+    // streaming merge, four partials per step so that their loads are in flight together;
+    // CTAs whose span is empty (G > total tiles) wrote nothing and are skipped
+    float M = -INFINITY, den = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float den = 0.f;
-    if (M > -INFINITY) {
-        for (int w = w0; w <= w1; ++w) {
-            if (span_begin(w, TT, G) >= span_begin(w + 1, TT, G)) continue;
-            const long long slot = w + b;
-            const float wt = expf(p.part_lse[slot * p.rows + r] - M);
-            const float4 v = *reinterpret_cast<const float4*>(p.part_o + (slot * p.rows + r) * V_DIM + d);
-            acc.x += wt * v.x; acc.y += wt * v.y; acc.z += wt * v.z; acc.w += wt * v.w;
-            den += wt;
+    for (int wb = w0; wb <= w1; wb += 4) {
+        float l[4];
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int w = wb + u;
+            const bool ok = w <= w1 && span_begin(w, TT, G) < span_begin(w + 1, TT, G);
+            const long long slot = (long long)(w + b) * p.rows + r;
+            l[u] = ok ? p.part_lse[slot] : -INFINITY;
+            v[u] = ok ? *reinterpret_cast<const float4*>(p.part_o + slot * V_DIM + d) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
+        const float m_new = fmaxf(fmaxf(fmaxf(l[0], l[1]), fmaxf(l[2], l[3])), M);
+        if (m_new > -INFINITY) {
+            const float f = M > -INFINITY ? expf(M - m_new) : 0.f;
+            acc.x *= f; acc.y *= f; acc.z *= f; acc.w *= f; den *= f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float wt = l[u] > -INFINITY ? expf(l[u] - m_new) : 0.f;
+                acc.x += wt * v[u].x; acc.y += wt * v[u].y; acc.z += wt * v[u].z; acc.w += wt * v[u].w;
+                den += wt;
+            }
+            M = m_new;
+        }
+    }
+    if (den > 0.f) {
         const float inv = 1.0f / den;
         acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
     }

@@ -42,6 +42,8 @@ struct MlaParams {
     float* part_o;                      // [G + batch - 1][rows][512] normalised partial O
     float* part_lse;                    // [G + batch - 1][rows]      natural-log LSE
     int* tile_prefix;                   // [batch + 1] exclusive prefix of tiles per sequence
+    uint8_t* q_split;                   // bf16 Q as two e4m3 planes [2][batch * rows][576] (tcgen05 kernels)
+    float* q_split_scale;               // [batch][rows / rows_per_cta] factor that undoes the planes' scaling
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -104,6 +106,36 @@ __device__ __forceinline__ long long slot_of(const MlaParams& p, int b, int seq_
     int pg = pos / p.page_size;
     return (long long)p.kv_indices[page_base + pg] * p.page_size + (pos - pg * p.page_size);
 }
+
+constexpr int WALK_TILE = 128;   // tokens per tile of the tcgen05 kernels (the walker below is theirs)
+
+// Position of one role inside the CTA's span of global tiles [t_begin, t_end): which sequence the
+// current tile belongs to, and that sequence's geometry.  Every role walks the span with its own copy.
+struct Walker {
+    int b, seq_t0, seq_t1;                  // sequence and its global tile range
+    int seq_base, seq_len, page_base, pos_off, tot_len;
+    int pair;                               // (CTA, sequence) pairs started so far, minus one
+    __device__ __forceinline__ void init(const int* prefix, int batch, int t_begin) {
+        b = seq_of_tile(prefix, batch, t_begin) - 1;
+        seq_t1 = -1;
+        pair = -1;
+    }
+    // Make the walker describe the sequence that owns global tile t (t only grows between calls).
+    // Returns true when t is the first tile of a new (CTA, sequence) pair.
+    __device__ __forceinline__ bool seek(const MlaParams& p, const int* prefix, int t) {
+        if (t < seq_t1) return false;
+        do { ++b; } while (prefix[b + 1] <= t);
+        seq_t0 = prefix[b];
+        seq_t1 = prefix[b + 1];
+        seq_base = p.kv_indptr[b];
+        seq_len = p.kv_indptr[b + 1] - seq_base;
+        page_base = p.kv_page_indptr ? p.kv_page_indptr[b] : seq_base;
+        pos_off = p.kv_pos_offset ? p.kv_pos_offset[b] : 0;
+        tot_len = p.kv_total_len ? p.kv_total_len[b] : seq_len;
+        ++pair;
+        return true;
+    }
+};
 
 // ---------------------------------------------------------------------------------------------
 // byte formats

@@ -1,0 +1,788 @@
+// tcgen05 / TMEM stage-1 MLA decode for the cache / query formats that need a pass over the data
+// before the tensor cores can take it: MXFP4 and hybrid caches (e2m1 codes + E8M0 block scales
+// become e4m3 operands) and bf16 queries (split into two e4m3 terms).  Same swap-AB formulation,
+// schedule, softmax and pipeline as mla_decode_sm100.cu (FP8 Q x FP8 KV), plus:
+//
+//  * "transform" warps between the gather and the MMA.  For a block-scaled cache the gather lands
+//    the raw codes of 32 tokens at a time in a small ring; the transform warps turn every 32-code
+//    block into 32 e4m3 bytes of the swizzled operand tile.  All blocks of a tile share one
+//    exponent frame: byte value = e2m1 * 2^(scale - E_tile + 6) with E_tile the largest E8M0 byte of
+//    the tile, which is exact in e4m3 for blocks up to 14 binades below the largest.  2^(E_tile - 133)
+//    is applied to the scores as a scalar and carried into O through a running exponent E_run
+//    (O is rescaled in TMEM when a later tile has a larger frame, like the softmax re-centering).
+//  * bf16 Q: a small kernel ahead of this one writes every group of N query rows as Q = (hi + lo/16) / s
+//    with hi, lo in e4m3 and s a power of two per group; the QK MMA then has 2N columns and the
+//    softmax adds the two halves.  (No tensor-core kind mixes bf16 with fp8 / fp4 operands.)
+//  * hybrid cache: the 64 rope dims are e4m3 with a per-tensor scale that is not a power of two,
+//    so their QK k-steps accumulate into a second set of TMEM columns and the softmax adds
+//    a_lat * S_lat + a_rope * S_rope.  The rope bytes go from HBM straight into the operand tile.
+//
+// Operand tile: four 128-byte-wide panels (dims 0..511, 128B swizzle; read K-major by QK and MN-major
+// by PV) and one 64-byte-wide panel (dims 512..575, 64B swizzle; QK only).
+// Roles: warps 0-3 softmax / epilogue, warp 4 MMA issue, then PW gather warps, then XW transform warps.
+// Role in the reference: the MXFP4 split-KV stage-1 kernels (mixed-mla/submission.py:122-250,
+// mixed-mla/versions/hip_mxfp4_v5/submission.py:214-656) and their block decode
+// (mixed-mla/triton_mla_mxfp4.py:20-67).
+#include "sm100_ptx.cuh"
+
+namespace b200mla {
+namespace sm100x {
+
+using namespace sm100;
+
+constexpr int TILE = 128;                 // tokens per tile = UMMA M
+constexpr int RAW_TOK = 32;               // tokens per raw buffer
+constexpr int NS = 2;                     // operand tile stages
+constexpr int PANEL_BYTES = TILE * 128;
+constexpr int ROPE_PANEL_BYTES = TILE * 64;
+constexpr int STAGE_BYTES = 4 * PANEL_BYTES + ROPE_PANEL_BYTES;    // 72 KB
+constexpr int SMEM_LIMIT = 232448;        // opt-in shared memory per CTA
+constexpr int RB_MAX = 6;
+constexpr float RECENTER = 4.0f;          // log2 units
+constexpr float P_SCALE_LOG2 = 4.0f;      // probabilities are stored multiplied by 2^4
+constexpr int E_BIAS = 127 + 6;           // operand bytes of a block-scaled tile are in units of 2^(E_tile - E_BIAS)
+
+template <int N, int KVFMT, int QFMT>
+struct Cfg {
+    static constexpr bool QSPLIT = QFMT == Q_BF16;
+    static constexpr bool XF = KVFMT != KV_E4M3;
+    static constexpr bool ROPE_SEP = KVFMT == KV_HYBRID;
+    static constexpr int NQ = N * (QSPLIT ? 2 : 1);               // Q rows in shared memory = columns of one S accumulator
+    static constexpr int SC = NQ * (ROPE_SEP ? 2 : 1);            // S columns per buffer
+    static constexpr int PW = XF ? (N == 16 ? 4 : 2) : (N == 16 ? 8 : 4);
+    static constexpr int XW = XF ? 4 : 0;
+    static constexpr int PRODUCERS = 32 * PW, XT = 32 * XW;
+    static constexpr int THREADS = 160 + PRODUCERS + XT;
+    static constexpr int NB = KVFMT == KV_MXFP4 ? 18 : 16;        // 32-code blocks per cache row
+    static constexpr int PAIRS = NB / 2;
+    static constexpr int RAW_ROW = NB * 16;                       // bytes of codes per row
+    static constexpr int RAW_BYTES = RAW_TOK * RAW_ROW;
+    static constexpr int Q_PANEL_BYTES = NQ * 128;
+    static constexpr int Q_BYTES = NQ * QK_DIM;                   // four 128B-swizzled panels and one 64B-swizzled
+    static constexpr int P_CHUNKS = 2 * N / 16;
+    static constexpr int P_BUF_BYTES = P_CHUNKS * TILE * 16;
+    static constexpr int MISC_RESERVE = 4096;                     // Misc + the tile prefix of ~700 sequences
+    static constexpr int FIXED = NS * STAGE_BYTES + Q_BYTES + 2 * P_BUF_BYTES + MISC_RESERVE;
+    static constexpr int RB_FIT = XF ? (SMEM_LIMIT - FIXED) / RAW_BYTES : 0;
+    static constexpr int RB = RB_FIT > RB_MAX ? RB_MAX : RB_FIT;  // raw buffers
+    static constexpr int OFF_Q = NS * STAGE_BYTES;
+    static constexpr int OFF_P = OFF_Q + Q_BYTES;
+    static constexpr int OFF_RAW = OFF_P + 2 * P_BUF_BYTES;
+    static constexpr int OFF_MISC = OFF_RAW + RB * RAW_BYTES;
+    static constexpr int TMEM_O = 2 * SC;
+    static constexpr int TMEM_NEED = 2 * SC + 8 * N;
+    static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
+    static constexpr int KV_FULL_COUNT = XF ? XT + (ROPE_SEP ? PRODUCERS : 0) : PRODUCERS;
+    static constexpr int TASKS = XF ? TILE * PAIRS / XT : 0;      // (token, block pair) tasks of one transform thread per tile
+    static constexpr int QTASKS = RAW_TOK * PAIRS;                // tasks per raw buffer
+    static_assert(TMEM_NEED <= 512, "TMEM columns");
+    static_assert(!XF || RB >= 2, "raw ring");
+    static_assert(!XF || (TILE * PAIRS) % (XT > 0 ? XT : 1) == 0, "transform tasks");
+};
+
+struct Misc {
+    uint64_t raw_full[RB_MAX], raw_empty[RB_MAX];
+    uint64_t kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], p_empty[2];
+    uint64_t q_full, q_empty, o_free;
+    uint32_t tmem_base;
+    int abort_flag;
+    int tile_exp[NS];            // E_tile of the tile in each operand stage (block-scaled caches)
+    int slot[NS][TILE];
+    float red[4][32];            // softmax cross-warp exchange
+    int xred[2][8];              // transform cross-warp exchange
+};
+
+// 2^e as a float; 0 below the normal range
+__device__ __forceinline__ float pow2i(int e) {
+    return e < -126 ? 0.0f : __int_as_float((min(e, 127) + 127) << 23);
+}
+
+// 32 e2m1 codes (one uint4, even element in the low nibble) -> 32 e4m3 bytes, value = code * 2^k.
+// Magnitudes go through an 8-entry byte table built for this block's k (the conversion rounds or
+// flushes the entries that e4m3 cannot hold exactly); signs move from nibble bit 3 to byte bit 7.
+__device__ __forceinline__ void dequant_block(const uint4& v, int k, uint4& lo, uint4& hi) {
+    const float sc = pow2i(max(k, -40));
+    const uint32_t t0 = pack_e4m3x4(0.0f, 0.5f * sc, sc, 1.5f * sc);
+    const uint32_t t1 = pack_e4m3x4(2.0f * sc, 3.0f * sc, 4.0f * sc, 6.0f * sc);
+    auto four = [&](uint32_t nib16) -> uint32_t {          // four codes in the low 16 bits -> four bytes
+        const uint32_t mag = __byte_perm(t0, t1, nib16 & 0x7777u);
+        const uint32_t y = __byte_perm(nib16 & 0x8888u, 0u, 0x1100u);   // bytes [b0, b0, b1, b1]
+        return mag | (y & 0x80008000u) | ((y & 0x00080008u) << 4);
+    };
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { o[2 * i] = four(w[i] & 0xffffu); o[2 * i + 1] = four(w[i] >> 16); }
+    lo = make_uint4(o[0], o[1], o[2], o[3]);
+    hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// byte offset inside an operand stage of the 16-byte column c (0..35) of token tok
+__device__ __forceinline__ uint32_t operand_offset(int tok, int c) {
+    return c < 32 ? (uint32_t)((c >> 3) * PANEL_BYTES + tok * 128 + (((c & 7) ^ (tok & 7)) << 4))
+                  : (uint32_t)(4 * PANEL_BYTES + tok * 64 + (((c - 32) ^ ((tok >> 1) & 3)) << 4));
+}
+
+template <int N, int KVFMT, int QFMT>
+__global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm100x_kernel(const MlaParams p, int* status) {
+    using C = Cfg<N, KVFMT, QFMT>;
+    constexpr int PRODUCERS = C::PRODUCERS, XT = C::XT, THREADS = C::THREADS, NQ = C::NQ;
+    constexpr int RB = C::RB > 0 ? C::RB : 1;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    Misc& ms = *reinterpret_cast<Misc*>(smem + C::OFF_MISC);
+    int* prefix = reinterpret_cast<int*>(smem + C::OFF_MISC + sizeof(Misc));
+    const uint32_t smem_base = smem_u32(smem);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int w = blockIdx.x, G = p.num_ctas;
+    const int row0 = blockIdx.y * N;
+
+    if (tid == 0) {
+        for (int i = 0; i < RB_MAX; ++i) { mbar_init(&ms.raw_full[i], PRODUCERS); mbar_init(&ms.raw_empty[i], XT > 0 ? XT : 1); }
+        for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], C::KV_FULL_COUNT); mbar_init(&ms.kv_empty[i], 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128);
+            mbar_init(&ms.p_full[i], 128); mbar_init(&ms.p_empty[i], 1);
+        }
+        mbar_init(&ms.q_full, PRODUCERS); mbar_init(&ms.q_empty, 1);
+        mbar_init(&ms.o_free, 128);
+        ms.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) { tmem_alloc(&ms.tmem_base, C::TMEM_COLS); tmem_relinquish(); }
+    build_tile_prefix(p.kv_indptr, p.batch, TILE, prefix);       // ends with __syncthreads()
+    tc_fence_after();
+    const uint32_t tmem = ms.tmem_base;
+    const int TT = prefix[p.batch];
+    if (w == 0 && blockIdx.y == 0)
+        for (int i = tid; i <= p.batch; i += THREADS) p.tile_prefix[i] = prefix[i];
+
+    const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
+    const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
+    volatile int* abort_flag = &ms.abort_flag;
+
+    if (n_total > 0) {
+        if (warp >= 5 && warp < 5 + C::PW) {
+            // =========================== gather ===========================
+            const int pt = tid - 160;
+            Walker wk; wk.init(prefix, p.batch, t_begin);
+            Walker wn = wk;                                       // one tile ahead, for the page-table prefetch
+            constexpr int SLOTS_PER_THREAD = (TILE + PRODUCERS - 1) / PRODUCERS;
+            int my_slot[SLOTS_PER_THREAD];
+            auto slots_for = [&](int g) {
+                if (g < n_total) wn.seek(p, prefix, t_begin + g);
+#pragma unroll
+                for (int k = 0; k < SLOTS_PER_THREAD; ++k) {
+                    const int tok = pt + k * PRODUCERS;
+                    const int pos = (t_begin + g - wn.seq_t0) * TILE + tok;
+                    my_slot[k] = (g < n_total && tok < TILE && pos < wn.seq_len)
+                                     ? (int)slot_of(p, wn.b, wn.seq_base, wn.page_base, pos) : -1;
+                }
+            };
+            // Copies `ncols` 16-byte columns of the rows [tok0, tok0 + ntok) of the tile in stage st: column c of a
+            // row comes from src_base + slot * stride + 16c and goes to dst_of(tok, c).  Consecutive threads take
+            // consecutive columns.  Rows past the end of the sequence are zero filled.
+            auto gather = [&](int st, int tok0, int ntok, int ncols, const uint8_t* src_base, long long stride, auto dst_of) {
+                const int total = ntok * ncols;
+                for (int id0 = pt; id0 < total; id0 += 8 * PRODUCERS) {   // batches of 8: slots first, then the copies
+                    int sl[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int id = id0 + u * PRODUCERS;
+                        sl[u] = id < total ? ms.slot[st][tok0 + id / ncols] : -2;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int id = id0 + u * PRODUCERS;
+                        if (sl[u] != -2) {
+                            const int tr = id / ncols, c = id - tr * ncols;
+                            const uint8_t* src = src_base + (long long)(sl[u] < 0 ? 0 : sl[u]) * stride + c * 16;
+                            cp_async16(dst_of(tok0 + tr, c), src, sl[u] < 0 ? 0u : 16u);
+                        }
+                    }
+                }
+            };
+            slots_for(0);
+            for (int g = 0; g < n_total; ++g) {
+                const int st = g % NS;
+                const bool first = wk.seek(p, prefix, t_begin + g);
+                // the gather threads are the only users of the slot table: the barrier pair orders the rewrite of
+                // stage st's entries after every thread's reads for tile g - NS
+                named_bar_sync(2, PRODUCERS);
+#pragma unroll
+                for (int k = 0; k < SLOTS_PER_THREAD; ++k)
+                    if (pt + k * PRODUCERS < TILE) ms.slot[st][pt + k * PRODUCERS] = my_slot[k];
+                named_bar_sync(2, PRODUCERS);
+                slots_for(g + 1);
+                const uint32_t stage_addr = smem_base + st * STAGE_BYTES;
+                if (!C::XF || C::ROPE_SEP) mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
+                if (!C::XF) {
+                    gather(st, 0, TILE, 36, p.kv_codes, p.kv_codes_stride,
+                           [&](int tok, int c) { return stage_addr + operand_offset(tok, c); });
+                    cp_async_mbar_arrive_noinc(&ms.kv_full[st]);
+                } else {
+                    if (C::ROPE_SEP) {                           // rope bytes are e4m3 already: straight into the rope panel
+                        gather(st, 0, TILE, 4, p.kv_rope, p.kv_rope_stride,
+                               [&](int tok, int c) { return stage_addr + operand_offset(tok, 32 + c); });
+                        cp_async_mbar_arrive_noinc(&ms.kv_full[st]);
+                    }
+#pragma unroll 1
+                    for (int q = 0; q < TILE / RAW_TOK; ++q) {
+                        const int gq = g * (TILE / RAW_TOK) + q, rb = gq % RB;
+                        mbar_wait(&ms.raw_empty[rb], gq / RB - 1, abort_flag);
+                        const uint32_t raw_addr = smem_base + C::OFF_RAW + rb * C::RAW_BYTES;
+                        gather(st, q * RAW_TOK, RAW_TOK, C::NB, p.kv_codes, p.kv_codes_stride,
+                               [&](int tok, int c) { return raw_addr + (uint32_t)((tok - q * RAW_TOK) * C::RAW_ROW + c * 16); });
+                        cp_async_mbar_arrive_noinc(&ms.raw_full[rb]);
+                    }
+                }
+                if (first) {
+                    // Q rows of the new sequence -> swizzled K-major panels.  Issued after the tile so that the wait for
+                    // the previous sequence's last QK does not hold the cache stream back.
+                    mbar_wait(&ms.q_empty, wk.pair - 1, abort_flag);
+                    const uint32_t q_addr = smem_base + C::OFF_Q;
+                    const long long plane = (long long)p.batch * p.rows * QK_DIM;   // split Q: hi plane, then lo plane
+                    for (int i = pt; i < NQ * 36; i += PRODUCERS) {
+                        const int r = i / 36, c = i - r * 36;
+                        const uint8_t* src;
+                        if (C::QSPLIT) {
+                            const int rr = r % N;
+                            src = p.q_split + (r / N) * plane + ((long long)wk.b * p.rows + row0 + rr) * QK_DIM + c * 16;
+                        } else {
+                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                            src = reinterpret_cast<const uint8_t*>(p.q) + (long long)(wk.b * p.q_len + j) * p.q_row_stride +
+                                  (long long)h * p.q_head_stride + c * 16;
+                        }
+                        const uint32_t dst = c < 32 ? q_addr + (c >> 3) * C::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)
+                                                    : q_addr + 4 * C::Q_PANEL_BYTES + r * 64 + (((c - 32) ^ ((r >> 1) & 3)) << 4);
+                        cp_async16(dst, src, 16u);
+                    }
+                    cp_async_mbar_arrive_noinc(&ms.q_full);
+                }
+            }
+            cp_async_wait_all();
+        } else if (warp == 4) {
+            // =========================== MMA issue (one lane) ===========================
+            if (lane == 0) {
+                constexpr uint32_t IDESC_QK = make_idesc(TILE, NQ, false, false);
+                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
+                // descriptor bases; per-MMA descriptors differ only in the start address
+                const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                              // + stage
+                const uint64_t d_qk_a_rope = make_desc(smem_base + 4 * PANEL_BYTES, 16, 512, SWIZZLE_64B);         // + stage
+                const uint64_t d_qk_b = make_desc(smem_base + C::OFF_Q, 16, 1024, SWIZZLE_128B);
+                const uint64_t d_qk_b_rope = make_desc(smem_base + C::OFF_Q + 4 * C::Q_PANEL_BYTES, 16, 512, SWIZZLE_64B);
+                const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);                     // + stage
+                const uint64_t d_pv_b = make_desc(smem_base + C::OFF_P, 128, TILE * 16, SWIZZLE_NONE);             // + buffer
+                Walker wq, wv;                                    // the QK stream runs ahead of the PV stream
+                wq.init(prefix, p.batch, t_begin);
+                wv = wq;
+                // S^T[128 tok x NQ] = K . Q^T for tile g; a hybrid cache keeps the rope dims in columns of their own
+                auto issue_qk = [&](int g) {
+                    const int st = g % NS, sb = g & 1;
+                    fence_proxy_async();       // cp.async wrote through the generic proxy; the MMA reads through the async proxy
+                    tc_fence_after();
+                    const uint32_t d_lat = tmem + sb * C::SC, d_rope = d_lat + (C::ROPE_SEP ? NQ : 0);
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        umma_f8(d_lat, desc_advance(d_qk_a, st * STAGE_BYTES + (k >> 2) * PANEL_BYTES + (k & 3) * 32),
+                                desc_advance(d_qk_b, (k >> 2) * C::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        umma_f8(d_rope, desc_advance(d_qk_a_rope, st * STAGE_BYTES + k * 32),
+                                desc_advance(d_qk_b_rope, k * 32), IDESC_QK, (!C::ROPE_SEP || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&ms.s_full[sb]);
+                    // last tile of this (CTA, sequence) pair: the Q buffer is free once these MMAs have run
+                    if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit(&ms.q_empty);
+                };
+                // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
+                auto issue_pv = [&](int g, bool first) {
+                    const int st = g % NS, pb = g & 1;
+                    tc_fence_after();
+                    const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
+                    const uint64_t b0 = desc_advance(d_pv_b, pb * C::P_BUF_BYTES);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            umma_f8(tmem + C::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
+                                    desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
+                        }
+                    }
+                    umma_commit(&ms.kv_empty[st]);
+                    umma_commit(&ms.p_empty[pb]);
+                };
+                // Event driven: PV(g) as soon as P(g) is published (it frees the tile for the next one), else
+                // QK of the next tile as soon as it is in place, its S buffer is free and its Q has landed.
+                int nq = 0, nv = 0;
+                bool q_first = wq.seek(p, prefix, t_begin), v_first = wv.seek(p, prefix, t_begin);
+                long long t_idle = clock64();
+                uint32_t spins = 0;
+                while (nv < n_total) {
+                    bool pv_ready = nv < nq && mbar_try_nb(&ms.p_full[nv & 1], (uint32_t)(nv / 2) & 1u);
+                    // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
+                    if (pv_ready && v_first && wv.pair > 0) pv_ready = mbar_try_nb(&ms.o_free, (uint32_t)(wv.pair - 1) & 1u);
+                    bool qk_ready = !pv_ready && nq < n_total &&
+                                    mbar_try_nb(&ms.kv_full[nq % NS], (uint32_t)(nq / NS) & 1u) &&
+                                    mbar_try_nb(&ms.s_empty[nq & 1], (uint32_t)(nq / 2 - 1) & 1u);
+                    if (qk_ready && q_first) qk_ready = mbar_try_nb(&ms.q_full, (uint32_t)wq.pair & 1u);
+                    if (!pv_ready && !qk_ready && (++spins & 63u) == 0u) {
+                        if (spins == 64u) t_idle = clock64();
+                        if (*abort_flag || clock64() - t_idle > WAIT_LIMIT_CYCLES) {
+                            *abort_flag = 1;        // give up waiting; issue the rest regardless so that every commit still arrives
+                            if (nq < n_total) qk_ready = true; else pv_ready = true;
+                        }
+                    }
+                    if (pv_ready) {
+                        issue_pv(nv, v_first);
+                        ++nv; spins = 0;
+                        if (nv < n_total) v_first = wv.seek(p, prefix, t_begin + nv);
+                    } else if (qk_ready) {
+                        issue_qk(nq);
+                        ++nq; spins = 0;
+                        if (nq < n_total) q_first = wq.seek(p, prefix, t_begin + nq);
+                    }
+                }
+            }
+        } else if (C::XF && warp >= 5 + C::PW) {
+            // =========================== transform (block-scaled caches) ===========================
+            // Task id = token * PAIRS + block pair, id = xt, xt + XT, ...: a thread turns two 16-byte code blocks
+            // into four 16-byte operand columns per task.  The E8M0 bytes come straight from global memory,
+            // fetched one tile ahead (and the page-table entries they hang off two tiles ahead).
+            constexpr int TASKS = C::TASKS > 0 ? C::TASKS : 1, PAIRS = C::PAIRS;
+            const int xt = tid - 160 - PRODUCERS, xwarp = xt >> 5;
+            Walker wn; wn.init(prefix, p.batch, t_begin);
+            const bool bs16 = ((reinterpret_cast<uintptr_t>(p.kv_bs) | (uintptr_t)p.kv_bs_stride) & 1u) == 0;
+            int slot_nxt[TASKS];
+            uint32_t sc_nxt[TASKS], sc_cur[TASKS];
+            auto load_slots = [&](int g) {
+                if (g < n_total) wn.seek(p, prefix, t_begin + g);
+#pragma unroll
+                for (int i = 0; i < TASKS; ++i) {
+                    const int tok = (xt + i * XT) / PAIRS;
+                    const int pos = (t_begin + g - wn.seq_t0) * TILE + tok;
+                    slot_nxt[i] = (g < n_total && pos < wn.seq_len) ? (int)slot_of(p, wn.b, wn.seq_base, wn.page_base, pos) : -1;
+                }
+            };
+            auto load_scales = [&]() {
+#pragma unroll
+                for (int i = 0; i < TASKS; ++i) {
+                    const int id = xt + i * XT, pair = id - (id / PAIRS) * PAIRS;
+                    uint32_t v = 0;
+                    if (slot_nxt[i] >= 0) {
+                        const uint8_t* s = p.kv_bs + (long long)slot_nxt[i] * p.kv_bs_stride + 2 * pair;
+                        v = bs16 ? (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(s))
+                                 : ((uint32_t)__ldg(s) | ((uint32_t)__ldg(s + 1) << 8));
+                    }
+                    sc_nxt[i] = v;
+                }
+            };
+            load_slots(0);
+            load_scales();
+            load_slots(1);
+            for (int g = 0; g < n_total; ++g) {
+                const int st = g % NS;
+#pragma unroll
+                for (int i = 0; i < TASKS; ++i) sc_cur[i] = sc_nxt[i];
+                if (g + 1 < n_total) load_scales();
+                load_slots(g + 2);
+                // exponent frame of the tile: the largest E8M0 byte of its 128 rows
+                uint32_t e = 0;
+#pragma unroll
+                for (int i = 0; i < TASKS; ++i) e = max(e, max(sc_cur[i] & 0xffu, sc_cur[i] >> 8));
+                e = __reduce_max_sync(0xffffffffu, e);
+                if (lane == 0) ms.xred[g & 1][xwarp] = (int)e;
+                named_bar_sync(3, XT);
+                int e_tile = 0;
+#pragma unroll
+                for (int i = 0; i < C::XW; ++i) e_tile = max(e_tile, ms.xred[g & 1][i]);
+                mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);      // the operand stage is free
+                if (xt == 0) ms.tile_exp[st] = e_tile;
+                unsigned char* stage = smem + st * STAGE_BYTES;
+                int q_cur = -1, rb = 0;
+#pragma unroll
+                for (int i = 0; i < TASKS; ++i) {
+                    const int id = xt + i * XT, q = id / C::QTASKS;     // warp-uniform: QTASKS is a multiple of 32
+                    if (q != q_cur) {
+                        if (q_cur >= 0) mbar_arrive(&ms.raw_empty[rb]);
+                        q_cur = q;
+                        const int gq = g * (TILE / RAW_TOK) + q;
+                        rb = gq % RB;
+                        mbar_wait(&ms.raw_full[rb], gq / RB, abort_flag);
+                    }
+                    const int tok = id / PAIRS, pair = id - tok * PAIRS;
+                    const unsigned char* raw = smem + C::OFF_RAW + rb * C::RAW_BYTES + (tok - q * RAW_TOK) * C::RAW_ROW + pair * 32;
+                    const uint4 v0 = *reinterpret_cast<const uint4*>(raw), v1 = *reinterpret_cast<const uint4*>(raw + 16);
+                    uint4 a, b;
+                    dequant_block(v0, (int)(sc_cur[i] & 0xffu) - e_tile + 6, a, b);
+                    *reinterpret_cast<uint4*>(stage + operand_offset(tok, 4 * pair)) = a;
+                    *reinterpret_cast<uint4*>(stage + operand_offset(tok, 4 * pair + 1)) = b;
+                    dequant_block(v1, (int)(sc_cur[i] >> 8) - e_tile + 6, a, b);
+                    *reinterpret_cast<uint4*>(stage + operand_offset(tok, 4 * pair + 2)) = a;
+                    *reinterpret_cast<uint4*>(stage + operand_offset(tok, 4 * pair + 3)) = b;
+                }
+                mbar_arrive(&ms.raw_empty[rb]);
+                fence_proxy_async();                                      // the MMA reads the tile through the async proxy
+                mbar_arrive(&ms.kv_full[st]);
+            }
+        } else if (warp < 4) {
+            // =========================== softmax / correction / epilogue (128 threads) ===========
+            const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+            Walker wk; wk.init(prefix, p.batch, t_begin);
+            const float q_tensor_scale = QFMT == Q_E4M3 ? __ldg(p.q_scale) : 1.0f;
+            const float kv_tensor_scale = KVFMT != KV_MXFP4 ? __ldg(p.kv_scale) : 1.0f;
+            float qk_base = 0.0f;          // sm_scale * log2(e) * (scale of this sequence's Q bytes)
+            int e_run = 0;                 // exponent frame of O (block-scaled caches)
+            // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key
+            float nm[N], l_acc[N];
+            // token position pos is visible to the rows of 16-column chunk q iff pos < lim[q]
+            // (heads is a multiple of 16, so the query index j is constant inside a chunk)
+            int lim[N / 16], lim_min = 0;
+            // per-column reduction over the 128 threads; result replicated in every thread
+            auto reduce_cols = [&](float (&v)[N], bool is_max) {
+#pragma unroll
+                for (int c = 0; c < N; ++c) {
+                    float x = v[c];
+#pragma unroll
+                    for (int o = 16; o >= 1; o >>= 1) {
+                        const float y = __shfl_xor_sync(0xffffffffu, x, o);
+                        x = is_max ? fmaxf(x, y) : x + y;
+                    }
+                    if (lane == 0) ms.red[warp][c] = x;
+                }
+                named_bar_sync(1, 128);
+#pragma unroll
+                for (int c = 0; c < N; ++c) {
+                    const float a0 = ms.red[0][c], a1 = ms.red[1][c], a2 = ms.red[2][c], a3 = ms.red[3][c];
+                    v[c] = is_max ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : (a0 + a1) + (a2 + a3);
+                }
+                named_bar_sync(1, 128);
+            };
+            for (int g = 0; g < n_total; ++g) {
+                const int sb = g & 1, st = g % NS;
+                const bool first = wk.seek(p, prefix, t_begin + g);
+                const bool last = t_begin + g + 1 == min(t_end, wk.seq_t1);
+                const int pos_first = (t_begin + g - wk.seq_t0) * TILE;
+                if (first) {
+#pragma unroll
+                    for (int c = 0; c < N; ++c) { nm[c] = INFINITY; l_acc[c] = 0.0f; }
+                    lim_min = 0x7fffffff;
+#pragma unroll
+                    for (int q = 0; q < N / 16; ++q) {
+                        const int j = (row0 + 16 * q) / p.heads;
+                        const int causal_lim = p.causal ? (wk.tot_len - p.q_len + j + 1 - wk.pos_off) : 0x7fffffff;
+                        lim[q] = min(wk.seq_len, causal_lim);
+                        lim_min = min(lim_min, lim[q]);
+                    }
+                    const float qs = C::QSPLIT ? __ldg(p.q_split_scale + (long long)wk.b * gridDim.y + blockIdx.y) : q_tensor_scale;
+                    qk_base = p.sm_scale * LOG2E * qs;
+                }
+                mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
+                tc_fence_after();
+                const int e_tile = C::XF ? *reinterpret_cast<volatile int*>(&ms.tile_exp[st]) : 0;
+                const float a_lat = C::XF ? qk_base * pow2i(e_tile - E_BIAS) : qk_base * kv_tensor_scale;
+                const float a_rope = qk_base * kv_tensor_scale;
+                // s[c] = score of (this thread's token, query row c) in log2 units
+                float s[N];
+                const uint32_t s_addr = tmem + lane_base + sb * C::SC;
+#pragma unroll
+                for (int c0 = 0; c0 < N; c0 += 16) {
+                    float v[16], vl[16], r[16], rl[16];
+                    tmem_ld16(s_addr + c0, v);
+                    if (C::QSPLIT) tmem_ld16(s_addr + N + c0, vl);
+                    if (C::ROPE_SEP) {
+                        tmem_ld16(s_addr + NQ + c0, r);
+                        if (C::QSPLIT) tmem_ld16(s_addr + NQ + N + c0, rl);
+                    }
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        float lat = v[c], rope = 0.0f;
+                        if (C::QSPLIT) lat = fmaf(vl[c], 0.0625f, lat);
+                        if (C::ROPE_SEP) { rope = r[c]; if (C::QSPLIT) rope = fmaf(rl[c], 0.0625f, rope); }
+                        s[c0 + c] = C::ROPE_SEP ? fmaf(rope, a_rope, lat * a_lat) : lat * a_lat;
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&ms.s_empty[sb]);
+
+                // x = log2-domain exponent of the stored probability: score - m_ref + P_SCALE_LOG2
+                const int pos = pos_first + tid;
+                const bool masked_tile = pos_first + TILE > lim_min;                 // uniform
+                float x[N];
+#pragma unroll
+                for (int c = 0; c < N; ++c) x[c] = s[c] + nm[c];
+                if (masked_tile) {
+#pragma unroll
+                    for (int c = 0; c < N; ++c) if (pos >= lim[c / 16]) x[c] = -INFINITY;
+                }
+                float xm = x[0];
+#pragma unroll
+                for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
+                const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
+                // a larger exponent frame than the one O is held in: O moves to the new frame
+                float o_frame = 1.0f;
+                if (C::XF) {
+                    if (first) e_run = e_tile;
+                    if (e_tile > e_run) { o_frame = pow2i(e_run - e_tile); e_run = e_tile; }
+                }
+                if (recenter || o_frame != 1.0f) {
+                    float f[N];
+                    bool any = o_frame != 1.0f;
+#pragma unroll
+                    for (int c = 0; c < N; ++c) f[c] = 1.0f;
+                    if (recenter) {
+                        float mx[N];
+#pragma unroll
+                        for (int c = 0; c < N; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : s[c];
+                        reduce_cols(mx, true);
+#pragma unroll
+                        for (int c = 0; c < N; ++c) {
+                            const float m_old = P_SCALE_LOG2 - nm[c];                 // -inf for a fresh column
+                            const float m_new = fmaxf(m_old, mx[c]);
+                            f[c] = (m_new == m_old) ? 1.0f : (m_old == -INFINITY ? 0.0f : ex2(m_old - m_new));
+                            any |= f[c] != 1.0f;
+                            nm[c] = P_SCALE_LOG2 - m_new;
+                            l_acc[c] *= f[c];
+                            x[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : s[c] + nm[c];
+                        }
+                    }
+                    if (!first && any) {
+                        // O holds the sequence's earlier tiles once PV(g-1) has completed; nothing else touches it until P(g) is published
+                        mbar_wait(&ms.p_empty[(g - 1) & 1], (g - 1) / 2, abort_flag);
+                        tc_fence_after();
+#pragma unroll
+                        for (int jb = 0; jb < 4; ++jb) {
+#pragma unroll
+                            for (int c0 = 0; c0 < 2 * N; c0 += 16) {
+                                float o[16];
+                                const uint32_t addr = tmem + lane_base + C::TMEM_O + jb * 2 * N + c0;
+                                tmem_ld16(addr, o);
+                                tmem_wait_ld();
+#pragma unroll
+                                for (int c = 0; c < 16; ++c) o[c] *= f[(c0 + c) % N] * o_frame;
+                                tmem_st16(addr, o);
+                            }
+                        }
+                        tmem_wait_st();
+                        tc_fence_before();
+                    }
+                }
+                // stored probability = p * 2^4 * 2^(e_tile - e_run): V bytes of this tile are in the frame e_tile, O in e_run
+                const float p_frame = C::XF ? pow2i(e_tile - e_run) : 1.0f;
+                // P(g) may overwrite its buffer once PV(g-2) has completed
+                mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
+                uint8_t* pbuf = smem + C::OFF_P + sb * C::P_BUF_BYTES;
+#pragma unroll
+                for (int c0 = 0; c0 < N; c0 += 16) {
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        float pv[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int c = c0 + q4 * 4 + k;
+                            pv[k] = ex2(x[c]);                                        // ex2(-inf) = 0 for masked keys
+                            l_acc[c] += pv[k];
+                            if (C::XF) pv[k] *= p_frame;
+                        }
+                        hi[q4] = pack_e4m3x4(pv[0], pv[1], pv[2], pv[3]);
+                        const float2 h01 = unpack_e4m3x2((uint16_t)(hi[q4] & 0xffffu)), h23 = unpack_e4m3x2((uint16_t)(hi[q4] >> 16));
+                        lo[q4] = pack_e4m3x4((pv[0] - h01.x) * 16.0f, (pv[1] - h01.y) * 16.0f,
+                                             (pv[2] - h23.x) * 16.0f, (pv[3] - h23.y) * 16.0f);
+                    }
+                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (TILE * 16) + tid * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (TILE * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                }
+                fence_proxy_async();
+                mbar_arrive(&ms.p_full[sb]);
+
+                if (last) {
+                    // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
+                    mbar_wait(&ms.p_empty[sb], g / 2, abort_flag);
+                    tc_fence_after();
+                    reduce_cols(l_acc, false);
+                    const bool whole = (t_begin <= wk.seq_t0) && (wk.seq_t1 <= t_end);
+                    const int slot = w + wk.b;
+                    const float out_scale = C::XF ? pow2i(e_run - E_BIAS) : kv_tensor_scale;
+                    float inv[N];
+#pragma unroll
+                    for (int c = 0; c < N; ++c) inv[c] = l_acc[c] > 0.0f ? __fdividef(out_scale, l_acc[c]) : 0.0f;
+                    // one output element per (row, dim): this thread owns dims tid, 128+tid, ... of every row
+                    const long long orow0 = whole ? ((long long)wk.b * p.rows + row0) : ((long long)slot * p.rows + row0);
+                    float* dst_f32 = whole ? p.out_o_f32 : p.part_o;
+                    __nv_bfloat16* dst_bf16 = whole ? p.out : nullptr;
+                    if (dst_f32) dst_f32 += orow0 * V_DIM + tid;
+                    if (dst_bf16) dst_bf16 += orow0 * V_DIM + tid;
+#pragma unroll
+                    for (int jb = 0; jb < 4; ++jb) {
+#pragma unroll
+                        for (int c0 = 0; c0 < N; c0 += 16) {
+                            float ohi[16], olo[16];
+                            tmem_ld16(tmem + lane_base + C::TMEM_O + jb * 2 * N + c0, ohi);
+                            tmem_ld16(tmem + lane_base + C::TMEM_O + jb * 2 * N + N + c0, olo);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) ohi[c] = fmaf(olo[c], 0.0625f, ohi[c]) * inv[c0 + c];
+                            if (dst_bf16) {
+#pragma unroll
+                                for (int c = 0; c < 16; ++c) dst_bf16[(c0 + c) * V_DIM + jb * 128] = __float2bfloat16_rn(ohi[c]);
+                            }
+                            if (dst_f32) {
+#pragma unroll
+                                for (int c = 0; c < 16; ++c) dst_f32[(c0 + c) * V_DIM + jb * 128] = ohi[c];
+                            }
+                        }
+                    }
+                    // O has been read: the next sequence's first PV may overwrite it
+                    tc_fence_before();
+                    mbar_arrive(&ms.o_free);
+                    if (tid < N) {
+                        float lsum = 0.0f, nmc = 0.0f;
+#pragma unroll
+                        for (int c = 0; c < N; ++c) if (c == tid) { lsum = l_acc[c]; nmc = nm[c]; }
+                        const float lse = lsum > 0.0f ? (log2f(lsum) - nmc) * LN2 : -INFINITY;
+                        if (whole) { if (p.out_lse) p.out_lse[(long long)wk.b * p.rows + row0 + tid] = lse; }
+                        else p.part_lse[(long long)slot * p.rows + row0 + tid] = lse;
+                    }
+                }
+            }
+        }
+    }
+
+    __syncthreads();
+    if (tid == 0 && ms.abort_flag) atomicMax(status, (int)ST_TIMEOUT);
+    if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+}
+
+// bf16 Q -> two e4m3 planes.  Block (group, sequence) takes the N query rows [group*N, group*N + N) of one
+// sequence, finds their largest magnitude, scales by the power of two s that puts it in [128, 256) and
+// writes hi = e4m3(q*s), lo = e4m3((q*s - hi) * 16); 1/s goes to inv_scale[sequence][group].
+// hi + lo/16 carries eight significant bits, as many as bf16 has.
+template <int N>
+__global__ void __launch_bounds__(256) q_split_kernel(const MlaParams p, uint8_t* planes, float* inv_scale) {
+    constexpr int VECS = N * (QK_DIM / 8), PER = (VECS + 255) / 256;
+    const int b = blockIdx.y, row0 = blockIdx.x * N, tid = threadIdx.x;
+    __shared__ float red[8];
+    uint4 v[PER];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int id = tid + i * 256;
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (id < VECS) {
+            const int r = id / (QK_DIM / 8), c8 = (id - r * (QK_DIM / 8)) * 8;
+            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+            v[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                         (long long)(b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c8));
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(h2[k]);
+                amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((tid & 31) == 0) red[tid >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+    // exponent of amax (clamped so that both s and 1/s stay normal); zero rows: s = 1
+    int e = ((__float_as_int(amax) >> 23) & 0xff) - 127;
+    e = amax > 0.0f ? max(-100, min(e, 100)) : 7;
+    const float s = __int_as_float((7 - e + 127) << 23);
+    if (tid == 0) inv_scale[(long long)b * gridDim.x + blockIdx.x] = __int_as_float((e - 7 + 127) << 23);
+    const long long plane = (long long)p.batch * p.rows * QK_DIM;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int id = tid + i * 256;
+        if (id < VECS) {
+            const int r = id / (QK_DIM / 8), c8 = (id - r * (QK_DIM / 8)) * 8;
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+            float f[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 t = __bfloat1622float2(h2[k]); f[2 * k] = t.x * s; f[2 * k + 1] = t.y * s; }
+            uint32_t hi[2], lo[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                hi[k] = sm100::pack_e4m3x4(f[4 * k], f[4 * k + 1], f[4 * k + 2], f[4 * k + 3]);
+                const float2 h01 = sm100::unpack_e4m3x2((uint16_t)(hi[k] & 0xffffu)), h23 = sm100::unpack_e4m3x2((uint16_t)(hi[k] >> 16));
+                lo[k] = sm100::pack_e4m3x4((f[4 * k] - h01.x) * 16.0f, (f[4 * k + 1] - h01.y) * 16.0f,
+                                           (f[4 * k + 2] - h23.x) * 16.0f, (f[4 * k + 3] - h23.y) * 16.0f);
+            }
+            uint8_t* dst = planes + ((long long)b * p.rows + row0 + r) * QK_DIM + c8;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(hi[0], hi[1]);
+            *reinterpret_cast<uint2*>(dst + plane) = make_uint2(lo[0], lo[1]);
+        }
+    }
+}
+
+}  // namespace sm100x
+
+namespace {
+
+template <int N, int KVFMT, int QFMT>
+size_t smem_need(int batch) {
+    return (size_t)sm100x::Cfg<N, KVFMT, QFMT>::OFF_MISC + sizeof(sm100x::Misc) + (size_t)(batch + 1) * sizeof(int);
+}
+
+template <int N, int KVFMT, int QFMT>
+cudaError_t launch_cfg(const MlaParams& p, int* status, cudaStream_t stream, bool dry_run, bool* fits) {
+    using C = sm100x::Cfg<N, KVFMT, QFMT>;
+    const size_t smem = smem_need<N, KVFMT, QFMT>(p.batch);
+    if (fits) *fits = smem <= (size_t)sm100x::SMEM_LIMIT;
+    if (dry_run) return cudaSuccess;
+    if (smem > (size_t)sm100x::SMEM_LIMIT) return cudaErrorInvalidConfiguration;
+    if (QFMT == Q_BF16) {
+        sm100x::q_split_kernel<N><<<dim3(p.rows / N, p.batch), 256, 0, stream>>>(p, p.q_split, p.q_split_scale);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    cudaError_t e = cudaFuncSetAttribute(sm100x::mla_decode_sm100x_kernel<N, KVFMT, QFMT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    dim3 grid(p.num_ctas, p.rows / N);
+    sm100x::mla_decode_sm100x_kernel<N, KVFMT, QFMT><<<grid, C::THREADS, smem, stream>>>(p, status);
+    return cudaGetLastError();
+}
+
+template <int N>
+cudaError_t dispatch_formats(const MlaParams& p, int* status, cudaStream_t stream, bool dry_run, bool* fits) {
+    if (p.q_format == Q_BF16) {
+        if (p.kv_format == KV_E4M3) return launch_cfg<N, KV_E4M3, Q_BF16>(p, status, stream, dry_run, fits);
+        if (p.kv_format == KV_MXFP4) return launch_cfg<N, KV_MXFP4, Q_BF16>(p, status, stream, dry_run, fits);
+        return launch_cfg<N, KV_HYBRID, Q_BF16>(p, status, stream, dry_run, fits);
+    }
+    if (p.kv_format == KV_MXFP4) return launch_cfg<N, KV_MXFP4, Q_E4M3>(p, status, stream, dry_run, fits);
+    if (p.kv_format == KV_HYBRID) return launch_cfg<N, KV_HYBRID, Q_E4M3>(p, status, stream, dry_run, fits);
+    if (fits) *fits = false;                                      // e4m3 x e4m3 belongs to the plain tcgen05 kernel
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+int sm100x_rows_per_cta(const MlaParams& p) { return p.rows % 32 == 0 ? 32 : 16; }
+
+// Every format pair except e4m3 Q x e4m3 cache; the tile-prefix table must fit beside the rings.
+bool sm100x_supported(const MlaParams& p) {
+    if (p.rows % 16 != 0 || (p.q_format == Q_E4M3 && p.kv_format == KV_E4M3)) return false;
+    bool fits = false;
+    if (sm100x_rows_per_cta(p) == 32) dispatch_formats<32>(p, nullptr, nullptr, true, &fits);
+    else dispatch_formats<16>(p, nullptr, nullptr, true, &fits);
+    return fits;
+}
+
+// bytes of the split-Q planes and of their per-group scales for a problem of this size
+long long sm100x_q_split_bytes(int batch, int rows) { return 2LL * batch * rows * QK_DIM; }
+long long sm100x_q_scale_bytes(int batch, int rows) { return (long long)batch * (rows / 16) * 4; }
+
+cudaError_t launch_sm100x(const MlaParams& p, int* status, cudaStream_t stream) {
+    return p.rows_per_cta == 32 ? dispatch_formats<32>(p, status, stream, false, nullptr)
+                                : dispatch_formats<16>(p, status, stream, false, nullptr);
+}
+
+}  // namespace b200mla
