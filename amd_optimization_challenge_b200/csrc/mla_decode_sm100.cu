@@ -56,7 +56,7 @@ __device__ long long* g_trace = nullptr;
 // ----------------------------------------------------------------------------------------------
 template <int N>
 struct Layout {
-    static constexpr int PRODUCER_WARPS = (N == 16) ? 8 : 2;     // fewer gather warps leave registers for N = 32
+    static constexpr int PRODUCER_WARPS = (N == 16) ? 11 : 2;    // 512 threads at 128 registers; N = 32 needs the registers
     static constexpr int PRODUCERS = 32 * PRODUCER_WARPS;
     static constexpr int THREADS = 160 + PRODUCERS;
     static constexpr int Q_PANEL_BYTES = N * 128;

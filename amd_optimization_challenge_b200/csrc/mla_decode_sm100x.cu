@@ -4,12 +4,13 @@
 // schedule, softmax and pipeline as mla_decode_sm100.cu (FP8 Q x FP8 KV), plus:
 //
 //  * "transform" warps between the gather and the MMA.  For a block-scaled cache the gather lands
-//    the raw codes of 32 tokens at a time in a small ring; the transform warps turn every 32-code
-//    block into 32 e4m3 bytes of the swizzled operand tile.  All blocks of a tile share one
-//    exponent frame: byte value = e2m1 * 2^(scale - E_tile + 6) with E_tile the largest E8M0 byte of
-//    the tile, which is exact in e4m3 for blocks up to 14 binades below the largest.  2^(E_tile - 133)
-//    is applied to the scores as a scalar and carried into O through a running exponent E_run
-//    (O is rescaled in TMEM when a later tile has a larger frame, like the softmax re-centering).
+//    the raw codes and E8M0 bytes of 16 tokens at a time (a unit) in a ring; a transform warp turns
+//    every 32-code block of a unit into 32 e4m3 bytes of the swizzled operand tile.  All blocks of a
+//    unit share one exponent frame: byte value = e2m1 * 2^(scale - E_unit + 6) with E_unit the largest
+//    E8M0 byte of the unit, which is exact in e4m3 for blocks up to 14 binades below the largest.
+//    The softmax thread of a token applies 2^(E_unit - 133) to its scores and 2^(E_unit - E_run) to
+//    its probabilities, E_run being the frame O is held in (O is rescaled in TMEM when a later tile
+//    has a larger frame, like the softmax re-centering).
 //  * bf16 Q: a small kernel ahead of this one writes every group of N query rows as Q = (hi + lo/16) / s
 //    with hi, lo in e4m3 and s a power of two per group; the QK MMA then has 2N columns and the
 //    softmax adds the two halves.  (No tensor-core kind mixes bf16 with fp8 / fp4 operands.)
@@ -31,16 +32,23 @@ namespace sm100x {
 using namespace sm100;
 
 constexpr int TILE = 128;                 // tokens per tile = UMMA M
-constexpr int RAW_TOK = 32;               // tokens per raw buffer
+constexpr int UNIT_TOK = 16;              // tokens per raw unit
 constexpr int NS = 2;                     // operand tile stages
 constexpr int PANEL_BYTES = TILE * 128;
 constexpr int ROPE_PANEL_BYTES = TILE * 64;
 constexpr int STAGE_BYTES = 4 * PANEL_BYTES + ROPE_PANEL_BYTES;    // 72 KB
 constexpr int SMEM_LIMIT = 232448;        // opt-in shared memory per CTA
-constexpr int RB_MAX = 6;
 constexpr float RECENTER = 4.0f;          // log2 units
 constexpr float P_SCALE_LOG2 = 4.0f;      // probabilities are stored multiplied by 2^4
 constexpr int E_BIAS = 127 + 6;           // operand bytes of a block-scaled tile are in units of 2^(E_tile - E_BIAS)
+
+// Optional timeline instrumentation (compiled in only with -DB200MLA_TRACE; development aid).
+#ifdef B200MLA_TRACE
+__device__ long long* g_trace = nullptr;
+#define TRACE(id, tile) do { if (g_trace && blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_trace[(tile) * 16 + (id)] = clock64(); } while (0)
+#else
+#define TRACE(id, tile) do { } while (0)
+#endif
 
 template <int N, int KVFMT, int QFMT>
 struct Cfg {
@@ -49,47 +57,46 @@ struct Cfg {
     static constexpr bool ROPE_SEP = KVFMT == KV_HYBRID;
     static constexpr int NQ = N * (QSPLIT ? 2 : 1);               // Q rows in shared memory = columns of one S accumulator
     static constexpr int SC = NQ * (ROPE_SEP ? 2 : 1);            // S columns per buffer
-    static constexpr int PW = XF ? (N == 16 ? 4 : 2) : (N == 16 ? 8 : 4);
-    static constexpr int XW = XF ? 4 : 0;
+    static constexpr int PW = XF ? 1 : (N == 16 ? 8 : 4);         // with transform warps the gather role only moves Q and rope bytes
+    static constexpr int XW = XF ? (N == 16 ? 8 : 4) : 0;
     static constexpr int PRODUCERS = 32 * PW, XT = 32 * XW;
     static constexpr int THREADS = 160 + PRODUCERS + XT;
     static constexpr int NB = KVFMT == KV_MXFP4 ? 18 : 16;        // 32-code blocks per cache row
-    static constexpr int PAIRS = NB / 2;
     static constexpr int RAW_ROW = NB * 16;                       // bytes of codes per row
-    static constexpr int RAW_BYTES = RAW_TOK * RAW_ROW;
+    static constexpr int PITCH = RAW_ROW + 16;                    // row pitch in a landing buffer: eight rows hit eight bank groups
+    static constexpr int OFF_UNIT_SCALES = UNIT_TOK * PITCH;      // 24 bytes per row: the aligned words around its E8M0 bytes
+    static constexpr int UNIT_BYTES = OFF_UNIT_SCALES + UNIT_TOK * 24;
     static constexpr int Q_PANEL_BYTES = NQ * 128;
     static constexpr int Q_BYTES = NQ * QK_DIM;                   // four 128B-swizzled panels and one 64B-swizzled
     static constexpr int P_CHUNKS = 2 * N / 16;
     static constexpr int P_BUF_BYTES = P_CHUNKS * TILE * 16;
     static constexpr int MISC_RESERVE = 4096;                     // Misc + the tile prefix of ~700 sequences
     static constexpr int FIXED = NS * STAGE_BYTES + Q_BYTES + 2 * P_BUF_BYTES + MISC_RESERVE;
-    static constexpr int RB_FIT = XF ? (SMEM_LIMIT - FIXED) / RAW_BYTES : 0;
-    static constexpr int RB = RB_FIT > RB_MAX ? RB_MAX : RB_FIT;  // raw buffers
+    // Landing buffers of the transform warps: S per warp, private to it
+    static constexpr int RB_FIT = XF ? (SMEM_LIMIT - FIXED) / UNIT_BYTES : 0;
+    static constexpr int S = !XF ? 0 : (RB_FIT >= 2 * XW ? 2 : 1);
+    static constexpr int RB = XW * S;
     static constexpr int OFF_Q = NS * STAGE_BYTES;
     static constexpr int OFF_P = OFF_Q + Q_BYTES;
     static constexpr int OFF_RAW = OFF_P + 2 * P_BUF_BYTES;
-    static constexpr int OFF_MISC = OFF_RAW + RB * RAW_BYTES;
+    static constexpr int OFF_MISC = OFF_RAW + RB * UNIT_BYTES;
     static constexpr int TMEM_O = 2 * SC;
     static constexpr int TMEM_NEED = 2 * SC + 8 * N;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
-    static constexpr int KV_FULL_COUNT = XF ? XT + (ROPE_SEP ? PRODUCERS : 0) : PRODUCERS;
-    static constexpr int TASKS = XF ? TILE * PAIRS / XT : 0;      // (token, block pair) tasks of one transform thread per tile
-    static constexpr int QTASKS = RAW_TOK * PAIRS;                // tasks per raw buffer
+    static constexpr int KV_FULL_COUNT = XF ? 32 * XW + (ROPE_SEP ? PRODUCERS : 0) : PRODUCERS;
     static_assert(TMEM_NEED <= 512, "TMEM columns");
-    static_assert(!XF || RB >= 2, "raw ring");
-    static_assert(!XF || (TILE * PAIRS) % (XT > 0 ? XT : 1) == 0, "transform tasks");
+    static_assert(!XF || RB_FIT >= XW, "landing buffers");
+    static_assert((UNIT_TOK * NB) % 32 == 0 && UNIT_BYTES % 16 == 0, "unit layout");
 };
 
 struct Misc {
-    uint64_t raw_full[RB_MAX], raw_empty[RB_MAX];
     uint64_t kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], p_empty[2];
     uint64_t q_full, q_empty, o_free;
     uint32_t tmem_base;
     int abort_flag;
-    int tile_exp[NS];            // E_tile of the tile in each operand stage (block-scaled caches)
+    int tile_exp[NS][TILE / UNIT_TOK];   // exponent frame of each 16-token unit of the tile in each operand stage
     int slot[NS][TILE];
     float red[4][32];            // softmax cross-warp exchange
-    int xred[2][8];              // transform cross-warp exchange
 };
 
 // 2^e as a float; 0 below the normal range
@@ -97,22 +104,35 @@ __device__ __forceinline__ float pow2i(int e) {
     return e < -126 ? 0.0f : __int_as_float((min(e, 127) + 127) << 23);
 }
 
-// 32 e2m1 codes (one uint4, even element in the low nibble) -> 32 e4m3 bytes, value = code * 2^k.
-// Magnitudes go through an 8-entry byte table built for this block's k (the conversion rounds or
-// flushes the entries that e4m3 cannot hold exactly); signs move from nibble bit 3 to byte bit 7.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// 32 e2m1 codes (one uint4, even element in the low nibble) -> 32 e4m3 bytes, value = code * 2^k, k <= 6.
+// Magnitudes: a byte permute through the 8-entry table of this block's k.  For k >= -5 every non-zero entry is a
+// normal e4m3 number, i.e. the k = 0 bytes plus 8k; below that the table comes from the rounding conversion
+// (entries that e4m3 cannot hold exactly are rounded or flushed).  Signs: a byte permute in sign-replication
+// mode turns nibble bit 3 (of the code word and of the word shifted by 4) into 0xff / 0x00 bytes.
 __device__ __forceinline__ void dequant_block(const uint4& v, int k, uint4& lo, uint4& hi) {
-    const float sc = pow2i(max(k, -40));
-    const uint32_t t0 = pack_e4m3x4(0.0f, 0.5f * sc, sc, 1.5f * sc);
-    const uint32_t t1 = pack_e4m3x4(2.0f * sc, 3.0f * sc, 4.0f * sc, 6.0f * sc);
-    auto four = [&](uint32_t nib16) -> uint32_t {          // four codes in the low 16 bits -> four bytes
-        const uint32_t mag = __byte_perm(t0, t1, nib16 & 0x7777u);
-        const uint32_t y = __byte_perm(nib16 & 0x8888u, 0u, 0x1100u);   // bytes [b0, b0, b1, b1]
-        return mag | (y & 0x80008000u) | ((y & 0x00080008u) << 4);
-    };
+    uint32_t t0, t1;
+    if (k >= -5) {
+        t0 = 0x3C383000u + (uint32_t)(k * 0x08080800);           // 0, .5, 1, 1.5
+        t1 = 0x4C484440u + (uint32_t)(k * 0x08080808);           // 2, 3, 4, 6
+    } else {
+        const float sc = pow2i(max(k, -40));
+        t0 = pack_e4m3x4(0.0f, 0.5f * sc, sc, 1.5f * sc);
+        t1 = pack_e4m3x4(2.0f * sc, 3.0f * sc, 4.0f * sc, 6.0f * sc);
+    }
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     uint32_t o[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { o[2 * i] = four(w[i] & 0xffffu); o[2 * i + 1] = four(w[i] >> 16); }
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t m = w[i] & 0x77777777u, w4 = w[i] << 4;
+        o[2 * i] = prmt(t0, t1, m) | (prmt(w4, w[i], 0xD9C8u) & 0x80808080u);
+        o[2 * i + 1] = prmt(t0, t1, m >> 16) | (prmt(w4, w[i], 0xFBEAu) & 0x80808080u);
+    }
     lo = make_uint4(o[0], o[1], o[2], o[3]);
     hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
@@ -126,8 +146,7 @@ __device__ __forceinline__ uint32_t operand_offset(int tok, int c) {
 template <int N, int KVFMT, int QFMT>
 __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm100x_kernel(const MlaParams p, int* status) {
     using C = Cfg<N, KVFMT, QFMT>;
-    constexpr int PRODUCERS = C::PRODUCERS, XT = C::XT, THREADS = C::THREADS, NQ = C::NQ;
-    constexpr int RB = C::RB > 0 ? C::RB : 1;
+    constexpr int PRODUCERS = C::PRODUCERS, THREADS = C::THREADS, NQ = C::NQ;
     extern __shared__ __align__(1024) unsigned char smem[];
     Misc& ms = *reinterpret_cast<Misc*>(smem + C::OFF_MISC);
     int* prefix = reinterpret_cast<int*>(smem + C::OFF_MISC + sizeof(Misc));
@@ -138,7 +157,6 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
     const int row0 = blockIdx.y * N;
 
     if (tid == 0) {
-        for (int i = 0; i < RB_MAX; ++i) { mbar_init(&ms.raw_full[i], PRODUCERS); mbar_init(&ms.raw_empty[i], XT > 0 ? XT : 1); }
         for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], C::KV_FULL_COUNT); mbar_init(&ms.kv_empty[i], 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128);
@@ -202,40 +220,38 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     }
                 }
             };
-            slots_for(0);
+            constexpr bool NEED_SLOTS = !C::XF || C::ROPE_SEP;        // does this role copy cache rows at all
+            if (NEED_SLOTS) slots_for(0);
             for (int g = 0; g < n_total; ++g) {
                 const int st = g % NS;
                 const bool first = wk.seek(p, prefix, t_begin + g);
-                // the gather threads are the only users of the slot table: the barrier pair orders the rewrite of
-                // stage st's entries after every thread's reads for tile g - NS
-                named_bar_sync(2, PRODUCERS);
+                if (NEED_SLOTS) {
+                    // the gather threads are the only users of the slot table: the barrier pair orders the rewrite of
+                    // stage st's entries after every thread's reads for tile g - NS
+                    named_bar_sync(2, PRODUCERS);
 #pragma unroll
-                for (int k = 0; k < SLOTS_PER_THREAD; ++k)
-                    if (pt + k * PRODUCERS < TILE) ms.slot[st][pt + k * PRODUCERS] = my_slot[k];
-                named_bar_sync(2, PRODUCERS);
-                slots_for(g + 1);
+                    for (int k = 0; k < SLOTS_PER_THREAD; ++k)
+                        if (pt + k * PRODUCERS < TILE) ms.slot[st][pt + k * PRODUCERS] = my_slot[k];
+                    named_bar_sync(2, PRODUCERS);
+                    slots_for(g + 1);
+                }
+                if (pt == 0) TRACE(0, g);
                 const uint32_t stage_addr = smem_base + st * STAGE_BYTES;
-                if (!C::XF || C::ROPE_SEP) mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
                 if (!C::XF) {
+                    mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
                     gather(st, 0, TILE, 36, p.kv_codes, p.kv_codes_stride,
                            [&](int tok, int c) { return stage_addr + operand_offset(tok, c); });
                     cp_async_mbar_arrive_noinc(&ms.kv_full[st]);
                 } else {
+                    // the codes and E8M0 bytes are fetched by the transform warps themselves
                     if (C::ROPE_SEP) {                           // rope bytes are e4m3 already: straight into the rope panel
+                        mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
                         gather(st, 0, TILE, 4, p.kv_rope, p.kv_rope_stride,
                                [&](int tok, int c) { return stage_addr + operand_offset(tok, 32 + c); });
                         cp_async_mbar_arrive_noinc(&ms.kv_full[st]);
                     }
-#pragma unroll 1
-                    for (int q = 0; q < TILE / RAW_TOK; ++q) {
-                        const int gq = g * (TILE / RAW_TOK) + q, rb = gq % RB;
-                        mbar_wait(&ms.raw_empty[rb], gq / RB - 1, abort_flag);
-                        const uint32_t raw_addr = smem_base + C::OFF_RAW + rb * C::RAW_BYTES;
-                        gather(st, q * RAW_TOK, RAW_TOK, C::NB, p.kv_codes, p.kv_codes_stride,
-                               [&](int tok, int c) { return raw_addr + (uint32_t)((tok - q * RAW_TOK) * C::RAW_ROW + c * 16); });
-                        cp_async_mbar_arrive_noinc(&ms.raw_full[rb]);
-                    }
                 }
+                if (pt == 0) TRACE(1, g);
                 if (first) {
                     // Q rows of the new sequence -> swizzled K-major panels.  Issued after the tile so that the wait for
                     // the previous sequence's last QK does not hold the cache stream back.
@@ -279,6 +295,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 // S^T[128 tok x NQ] = K . Q^T for tile g; a hybrid cache keeps the rope dims in columns of their own
                 auto issue_qk = [&](int g) {
                     const int st = g % NS, sb = g & 1;
+                    TRACE(6, g);
                     fence_proxy_async();       // cp.async wrote through the generic proxy; the MMA reads through the async proxy
                     tc_fence_after();
                     const uint32_t d_lat = tmem + sb * C::SC, d_rope = d_lat + (C::ROPE_SEP ? NQ : 0);
@@ -299,6 +316,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
                 auto issue_pv = [&](int g, bool first) {
                     const int st = g % NS, pb = g & 1;
+                    TRACE(7, g);
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
                     const uint64_t b0 = desc_advance(d_pv_b, pb * C::P_BUF_BYTES);
@@ -347,85 +365,120 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             }
         } else if (C::XF && warp >= 5 + C::PW) {
             // =========================== transform (block-scaled caches) ===========================
-            // Task id = token * PAIRS + block pair, id = xt, xt + XT, ...: a thread turns two 16-byte code blocks
-            // into four 16-byte operand columns per task.  The E8M0 bytes come straight from global memory,
-            // fetched one tile ahead (and the page-table entries they hang off two tiles ahead).
-            constexpr int TASKS = C::TASKS > 0 ? C::TASKS : 1, PAIRS = C::PAIRS;
-            const int xt = tid - 160 - PRODUCERS, xwarp = xt >> 5;
+            // Warp xw owns the 16-token units xw, xw + XW, ... of every tile and S private landing buffers.  For each
+            // unit it fetches the raw rows itself (16-byte cp.async of the codes, the aligned 8-byte words around the
+            // E8M0 bytes; rows past the end of the sequence are zero filled), moves a landed unit into registers,
+            // reuses the buffer for the unit S ahead at once, and then turns 32-code blocks into pairs of 16-byte
+            // columns of the operand tile.  Lane = (row lane % 16, block parity lane / 16): a quarter warp stores the
+            // same column of eight consecutive rows, which the swizzle spreads over all banks, and reads eight rows
+            // whose padded pitch does the same.  Each unit has its own exponent frame: its largest E8M0 byte.
+            constexpr int NBH = C::NB / 2;                                // blocks per lane per unit
+            constexpr int UPW = (TILE / UNIT_TOK) / (C::XW > 0 ? C::XW : 1);   // units per warp per tile
+            constexpr int S = C::S > 0 ? C::S : 1;
+            constexpr int CODE_IT = UNIT_TOK * C::NB / 32, PER = CODE_IT + 2;   // copy instructions per lane per unit: codes, E8M0 words
+            const int xw = warp - 5 - C::PW;
+            const int tok = lane & (UNIT_TOK - 1), par = lane >> 4;
+            const int J = n_total * UPW;                                  // units of this warp
             Walker wn; wn.init(prefix, p.batch, t_begin);
-            const bool bs16 = ((reinterpret_cast<uintptr_t>(p.kv_bs) | (uintptr_t)p.kv_bs_stride) & 1u) == 0;
-            int slot_nxt[TASKS];
-            uint32_t sc_nxt[TASKS], sc_cur[TASKS];
-            auto load_slots = [&](int g) {
-                if (g < n_total) wn.seek(p, prefix, t_begin + g);
-#pragma unroll
-                for (int i = 0; i < TASKS; ++i) {
-                    const int tok = (xt + i * XT) / PAIRS;
-                    const int pos = (t_begin + g - wn.seq_t0) * TILE + tok;
-                    slot_nxt[i] = (g < n_total && pos < wn.seq_len) ? (int)slot_of(p, wn.b, wn.seq_base, wn.page_base, pos) : -1;
-                }
+            // cache slot of row `tok` of this warp's unit j; -1 past the end of the sequence or of the span
+            auto fetch_slot = [&](int j) -> int {
+                if (j >= J) return -1;
+                const int g = j / UPW, k = xw + (j - g * UPW) * C::XW;
+                wn.seek(p, prefix, t_begin + g);
+                const int pos = (t_begin + g - wn.seq_t0) * TILE + k * UNIT_TOK + tok;
+                return pos < wn.seq_len ? (int)slot_of(p, wn.b, wn.seq_base, wn.page_base, pos) : -1;
             };
-            auto load_scales = [&]() {
+            // lane constants: where block par + 2i of row tok goes in unit 0 of an operand stage, and which
+            // (row, 16-byte column) each copy instruction of this lane moves (consecutive lanes, consecutive columns)
+            uint32_t st_off[NBH], cp_pk[CODE_IT];
 #pragma unroll
-                for (int i = 0; i < TASKS; ++i) {
-                    const int id = xt + i * XT, pair = id - (id / PAIRS) * PAIRS;
-                    uint32_t v = 0;
-                    if (slot_nxt[i] >= 0) {
-                        const uint8_t* s = p.kv_bs + (long long)slot_nxt[i] * p.kv_bs_stride + 2 * pair;
-                        v = bs16 ? (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(s))
-                                 : ((uint32_t)__ldg(s) | ((uint32_t)__ldg(s + 1) << 8));
-                    }
-                    sc_nxt[i] = v;
-                }
-            };
-            load_slots(0);
-            load_scales();
-            load_slots(1);
-            for (int g = 0; g < n_total; ++g) {
-                const int st = g % NS;
+            for (int i = 0; i < NBH; ++i) st_off[i] = operand_offset(tok, 2 * (par + 2 * i));
 #pragma unroll
-                for (int i = 0; i < TASKS; ++i) sc_cur[i] = sc_nxt[i];
-                if (g + 1 < n_total) load_scales();
-                load_slots(g + 2);
-                // exponent frame of the tile: the largest E8M0 byte of its 128 rows
-                uint32_t e = 0;
-#pragma unroll
-                for (int i = 0; i < TASKS; ++i) e = max(e, max(sc_cur[i] & 0xffu, sc_cur[i] >> 8));
-                e = __reduce_max_sync(0xffffffffu, e);
-                if (lane == 0) ms.xred[g & 1][xwarp] = (int)e;
-                named_bar_sync(3, XT);
-                int e_tile = 0;
-#pragma unroll
-                for (int i = 0; i < C::XW; ++i) e_tile = max(e_tile, ms.xred[g & 1][i]);
-                mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);      // the operand stage is free
-                if (xt == 0) ms.tile_exp[st] = e_tile;
-                unsigned char* stage = smem + st * STAGE_BYTES;
-                int q_cur = -1, rb = 0;
-#pragma unroll
-                for (int i = 0; i < TASKS; ++i) {
-                    const int id = xt + i * XT, q = id / C::QTASKS;     // warp-uniform: QTASKS is a multiple of 32
-                    if (q != q_cur) {
-                        if (q_cur >= 0) mbar_arrive(&ms.raw_empty[rb]);
-                        q_cur = q;
-                        const int gq = g * (TILE / RAW_TOK) + q;
-                        rb = gq % RB;
-                        mbar_wait(&ms.raw_full[rb], gq / RB, abort_flag);
-                    }
-                    const int tok = id / PAIRS, pair = id - tok * PAIRS;
-                    const unsigned char* raw = smem + C::OFF_RAW + rb * C::RAW_BYTES + (tok - q * RAW_TOK) * C::RAW_ROW + pair * 32;
-                    const uint4 v0 = *reinterpret_cast<const uint4*>(raw), v1 = *reinterpret_cast<const uint4*>(raw + 16);
-                    uint4 a, b;
-                    dequant_block(v0, (int)(sc_cur[i] & 0xffu) - e_tile + 6, a, b);
-                    *reinterpret_cast<uint4*>(stage + operand_offset(tok, 4 * pair)) = a;
-                    *reinterpret_cast<uint4*>(stage + operand_offset(tok, 4 * pair + 1)) = b;
-                    dequant_block(v1, (int)(sc_cur[i] >> 8) - e_tile + 6, a, b);
-                    *reinterpret_cast<uint4*>(stage + operand_offset(tok, 4 * pair + 2)) = a;
-                    *reinterpret_cast<uint4*>(stage + operand_offset(tok, 4 * pair + 3)) = b;
-                }
-                mbar_arrive(&ms.raw_empty[rb]);
-                fence_proxy_async();                                      // the MMA reads the tile through the async proxy
-                mbar_arrive(&ms.kv_full[st]);
+            for (int it = 0; it < CODE_IT; ++it) {
+                const int id = lane + 32 * it, tr = id / C::NB, col = id - tr * C::NB;
+                cp_pk[it] = (uint32_t)tr | ((uint32_t)(col * 16) << 4) | ((uint32_t)(tr * C::PITCH + col * 16) << 16);
             }
+            // copy instruction `it` (0..PER-1) of one unit into landing buffer `buf`; row_slot = fetch_slot of that unit
+            auto issue_part = [&](int buf, int row_slot, int it) {
+                const uint32_t unit_addr = smem_base + C::OFF_RAW + (xw * S + buf) * C::UNIT_BYTES;
+                if (it < CODE_IT) {
+                    const uint32_t pk = cp_pk[it];
+                    const int sl = __shfl_sync(0xffffffffu, row_slot, pk & 15u);
+                    cp_async16(unit_addr + (pk >> 16), p.kv_codes + (long long)max(sl, 0) * p.kv_codes_stride + ((pk >> 4) & 0xfffu),
+                               sl < 0 ? 0u : 16u);
+                } else {
+                    const int id = lane + 32 * (it - CODE_IT), tr = min(id / 3, UNIT_TOK - 1), wd = id - (id / 3) * 3;
+                    const int sl = __shfl_sync(0xffffffffu, row_slot, tr);
+                    const uintptr_t bs = reinterpret_cast<uintptr_t>(p.kv_bs + (long long)max(sl, 0) * p.kv_bs_stride);
+                    const int nwords = ((int)(bs & 7) + C::NB + 7) >> 3;   // only words that overlap the row are read
+                    if (id < UNIT_TOK * 3)
+                        cp_async8(unit_addr + C::OFF_UNIT_SCALES + tr * 24 + wd * 8, reinterpret_cast<const void*>((bs & ~(uintptr_t)7) + wd * 8),
+                                  (sl < 0 || wd >= nwords) ? 0u : 8u);
+                }
+            };
+            int held[S];                                                  // row slots of the units now in the buffers
+            int nxt = fetch_slot(0);
+#pragma unroll
+            for (int d = 0; d < S; ++d) {
+#pragma unroll
+                for (int it = 0; it < PER; ++it) issue_part(d, nxt, it);
+                cp_async_commit();
+                held[d] = nxt;
+                nxt = fetch_slot(d + 1);
+            }
+            for (int j = 0; j < J; ++j) {
+                const int g = j / UPW, ku = j - g * UPW, k = xw + ku * C::XW, st = g % NS, buf = j % S;
+                cp_async_wait_pending<S - 1>();                           // this lane's copies of unit j have landed
+                __syncwarp();                                             // ... and every other lane's
+                if (xw == 0 && lane == 0 && ku == 0) TRACE(4, g);
+                const unsigned char* unit = smem + C::OFF_RAW + (xw * S + buf) * C::UNIT_BYTES;
+                const int cur = S == 1 ? held[0] : (buf == 0 ? held[0] : held[S - 1]);
+                // the unit moves into registers: blocks par, par + 2, ... of row tok with their E8M0 bytes (a zero-filled
+                // row reads as codes 0, scale 0)
+                const int o = (int)(reinterpret_cast<uintptr_t>(p.kv_bs + (long long)max(cur, 0) * p.kv_bs_stride) & 7);
+                const unsigned char* sc_row = unit + C::OFF_UNIT_SCALES + tok * 24 + o + par;
+                uint32_t sc[NBH], e = 0;
+                uint4 v[NBH];
+#pragma unroll
+                for (int i = 0; i < NBH; ++i) {
+                    sc[i] = sc_row[2 * i];
+                    v[i] = *reinterpret_cast<const uint4*>(unit + tok * C::PITCH + (par + 2 * i) * 16);
+                    e = max(e, sc[i]);
+                }
+                __syncwarp();                                             // the buffer has been read by every lane
+                const int e_unit = (int)__reduce_max_sync(0xffffffffu, e);
+                if (ku == 0) {
+                    if (xw == 0 && lane == 0) TRACE(2, g);
+                    mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);          // the operand stage is free
+                    if (xw == 0 && lane == 0) TRACE(3, g);
+                }
+                if (lane == 0) ms.tile_exp[st][k] = e_unit;
+                // The arithmetic of unit j is interleaved with the copy instructions of unit j + S (an empty group past
+                // the end), which go into the buffer just read.
+                unsigned char* dst_lat = smem + st * STAGE_BYTES + k * (UNIT_TOK * 128);   // panels 0-3: 128-byte rows
+                unsigned char* dst_rope = smem + st * STAGE_BYTES + k * (UNIT_TOK * 64);   // rope panel: 64-byte rows
+                constexpr int IPT = (PER + NBH - 1) / NBH;                // copy instructions per block
+#pragma unroll
+                for (int i = 0; i < NBH; ++i) {
+#pragma unroll
+                    for (int q = 0; q < IPT; ++q)
+                        if (i * IPT + q < PER) issue_part(buf, nxt, i * IPT + q);
+                    uint4 a, b;
+                    dequant_block(v[i], (int)sc[i] - e_unit + 6, a, b);
+                    unsigned char* d = (2 * (2 * i) >= 32 ? dst_rope : dst_lat) + st_off[i];   // block par + 2i >= 16: rope dims
+                    *reinterpret_cast<uint4*>(d) = a;
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uintptr_t>(d) ^ 16) = b;
+                }
+                cp_async_commit();
+                if (S == 1 || buf == 0) held[0] = nxt; else held[S - 1] = nxt;
+                nxt = fetch_slot(j + S + 1);
+                if (ku == UPW - 1) {
+                    fence_proxy_async();                                  // the MMA reads the tile through the async proxy
+                    mbar_arrive(&ms.kv_full[st]);
+                    if (xw == 0 && lane == 0) TRACE(5, g);
+                }
+            }
+            cp_async_wait_all();
         } else if (warp < 4) {
             // =========================== softmax / correction / epilogue (128 threads) ===========
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
@@ -479,9 +532,17 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     qk_base = p.sm_scale * LOG2E * qs;
                 }
                 mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
+                if (tid == 0) TRACE(8, g);
                 tc_fence_after();
-                const int e_tile = C::XF ? *reinterpret_cast<volatile int*>(&ms.tile_exp[st]) : 0;
-                const float a_lat = C::XF ? qk_base * pow2i(e_tile - E_BIAS) : qk_base * kv_tensor_scale;
+                // exponent frames: e_unit of this thread's token, e_tile = the largest of the tile's units
+                int e_unit = 0, e_tile = 0;
+                if (C::XF) {
+                    const volatile int* te = ms.tile_exp[st];
+                    e_unit = te[tid / UNIT_TOK];
+#pragma unroll
+                    for (int i = 0; i < TILE / UNIT_TOK; ++i) e_tile = max(e_tile, te[i]);
+                }
+                const float a_lat = C::XF ? qk_base * pow2i(e_unit - E_BIAS) : qk_base * kv_tensor_scale;
                 const float a_rope = qk_base * kv_tensor_scale;
                 // s[c] = score of (this thread's token, query row c) in log2 units
                 float s[N];
@@ -569,8 +630,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                         tc_fence_before();
                     }
                 }
-                // stored probability = p * 2^4 * 2^(e_tile - e_run): V bytes of this tile are in the frame e_tile, O in e_run
-                const float p_frame = C::XF ? pow2i(e_tile - e_run) : 1.0f;
+                // stored probability = p * 2^4 * 2^(e_unit - e_run): this token's V bytes are in the frame e_unit, O in e_run
+                const float p_frame = C::XF ? pow2i(e_unit - e_run) : 1.0f;
                 // P(g) may overwrite its buffer once PV(g-2) has completed
                 mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
                 uint8_t* pbuf = smem + C::OFF_P + sb * C::P_BUF_BYTES;
@@ -597,6 +658,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 }
                 fence_proxy_async();
                 mbar_arrive(&ms.p_full[sb]);
+                if (tid == 0) TRACE(9, g);
 
                 if (last) {
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
@@ -770,6 +832,8 @@ int sm100x_rows_per_cta(const MlaParams& p) { return p.rows % 32 == 0 ? 32 : 16;
 // Every format pair except e4m3 Q x e4m3 cache; the tile-prefix table must fit beside the rings.
 bool sm100x_supported(const MlaParams& p) {
     if (p.rows % 16 != 0 || (p.q_format == Q_E4M3 && p.kv_format == KV_E4M3)) return false;
+    // the E8M0 rows are fetched as three aligned 8-byte words: they must start on an even address
+    if (p.kv_format != KV_E4M3 && ((reinterpret_cast<uintptr_t>(p.kv_bs) | (uintptr_t)p.kv_bs_stride) & 1u)) return false;
     bool fits = false;
     if (sm100x_rows_per_cta(p) == 32) dispatch_formats<32>(p, nullptr, nullptr, true, &fits);
     else dispatch_formats<16>(p, nullptr, nullptr, true, &fits);
@@ -779,6 +843,12 @@ bool sm100x_supported(const MlaParams& p) {
 // bytes of the split-Q planes and of their per-group scales for a problem of this size
 long long sm100x_q_split_bytes(int batch, int rows) { return 2LL * batch * rows * QK_DIM; }
 long long sm100x_q_scale_bytes(int batch, int rows) { return (long long)batch * (rows / 16) * 4; }
+
+#ifdef B200MLA_TRACE
+extern "C" int b200_mla_debug_set_trace_x(long long* ptr) {
+    return (int)cudaMemcpyToSymbol(sm100x::g_trace, &ptr, sizeof(ptr));
+}
+#endif
 
 cudaError_t launch_sm100x(const MlaParams& p, int* status, cudaStream_t stream) {
     return p.rows_per_cta == 32 ? dispatch_formats<32>(p, status, stream, false, nullptr)
