@@ -292,26 +292,34 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 Walker wq, wv;                                    // the QK stream runs ahead of the PV stream
                 wq.init(prefix, p.batch, t_begin);
                 wv = wq;
-                // S^T[128 tok x NQ] = K . Q^T for tile g; a hybrid cache keeps the rope dims in columns of their own
-                auto issue_qk = [&](int g) {
+                // S^T[128 tok x NQ] = K . Q^T for tile g; a hybrid cache keeps the rope dims in columns of their own.
+                // QK_PARTS > 1 would issue it in pieces with PVs in between; measured slower (alternating the two MMA
+                // shapes costs more than the PV gains), so it stays in one piece.
+                constexpr int QK_PARTS = 1;
+                auto issue_qk = [&](int g, int part) {
                     const int st = g % NS, sb = g & 1;
-                    TRACE(6, g);
-                    fence_proxy_async();       // cp.async wrote through the generic proxy; the MMA reads through the async proxy
-                    tc_fence_after();
+                    if (part == 0) {
+                        TRACE(6, g);
+                        fence_proxy_async();   // cp.async wrote through the generic proxy; the MMA reads through the async proxy
+                        tc_fence_after();
+                    }
                     const uint32_t d_lat = tmem + sb * C::SC, d_rope = d_lat + (C::ROPE_SEP ? NQ : 0);
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        umma_f8(d_lat, desc_advance(d_qk_a, st * STAGE_BYTES + (k >> 2) * PANEL_BYTES + (k & 3) * 32),
-                                desc_advance(d_qk_b, (k >> 2) * C::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < 18 / QK_PARTS; ++kk) {
+                        const int k = part * (18 / QK_PARTS) + kk;
+                        if (k < 16) {
+                            umma_f8(d_lat, desc_advance(d_qk_a, st * STAGE_BYTES + (k >> 2) * PANEL_BYTES + (k & 3) * 32),
+                                    desc_advance(d_qk_b, (k >> 2) * C::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
+                        } else {
+                            umma_f8(d_rope, desc_advance(d_qk_a_rope, st * STAGE_BYTES + (k - 16) * 32),
+                                    desc_advance(d_qk_b_rope, (k - 16) * 32), IDESC_QK, (!C::ROPE_SEP || k > 16) ? 1u : 0u);
+                        }
                     }
-#pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        umma_f8(d_rope, desc_advance(d_qk_a_rope, st * STAGE_BYTES + k * 32),
-                                desc_advance(d_qk_b_rope, k * 32), IDESC_QK, (!C::ROPE_SEP || k > 0) ? 1u : 0u);
+                    if (part == QK_PARTS - 1) {
+                        umma_commit(&ms.s_full[sb]);
+                        // last tile of this (CTA, sequence) pair: the Q buffer is free once these MMAs have run
+                        if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit(&ms.q_empty);
                     }
-                    umma_commit(&ms.s_full[sb]);
-                    // last tile of this (CTA, sequence) pair: the Q buffer is free once these MMAs have run
-                    if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit(&ms.q_empty);
                 };
                 // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
                 auto issue_pv = [&](int g, bool first) {
@@ -333,7 +341,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 };
                 // Event driven: PV(g) as soon as P(g) is published (it frees the tile for the next one), else
                 // QK of the next tile as soon as it is in place, its S buffer is free and its Q has landed.
-                int nq = 0, nv = 0;
+                int nq = 0, nv = 0, qk_part = 0;
                 bool q_first = wq.seek(p, prefix, t_begin), v_first = wv.seek(p, prefix, t_begin);
                 long long t_idle = clock64();
                 uint32_t spins = 0;
@@ -342,9 +350,10 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
                     if (pv_ready && v_first && wv.pair > 0) pv_ready = mbar_try_nb(&ms.o_free, (uint32_t)(wv.pair - 1) & 1u);
                     bool qk_ready = !pv_ready && nq < n_total &&
-                                    mbar_try_nb(&ms.kv_full[nq % NS], (uint32_t)(nq / NS) & 1u) &&
-                                    mbar_try_nb(&ms.s_empty[nq & 1], (uint32_t)(nq / 2 - 1) & 1u);
-                    if (qk_ready && q_first) qk_ready = mbar_try_nb(&ms.q_full, (uint32_t)wq.pair & 1u);
+                                    (qk_part > 0 ||
+                                     (mbar_try_nb(&ms.kv_full[nq % NS], (uint32_t)(nq / NS) & 1u) &&
+                                      mbar_try_nb(&ms.s_empty[nq & 1], (uint32_t)(nq / 2 - 1) & 1u) &&
+                                      (!q_first || mbar_try_nb(&ms.q_full, (uint32_t)wq.pair & 1u))));
                     if (!pv_ready && !qk_ready && (++spins & 63u) == 0u) {
                         if (spins == 64u) t_idle = clock64();
                         if (*abort_flag || clock64() - t_idle > WAIT_LIMIT_CYCLES) {
@@ -357,9 +366,13 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                         ++nv; spins = 0;
                         if (nv < n_total) v_first = wv.seek(p, prefix, t_begin + nv);
                     } else if (qk_ready) {
-                        issue_qk(nq);
-                        ++nq; spins = 0;
-                        if (nq < n_total) q_first = wq.seek(p, prefix, t_begin + nq);
+                        issue_qk(nq, qk_part);
+                        spins = 0;
+                        if (++qk_part == QK_PARTS) {
+                            qk_part = 0;
+                            ++nq;
+                            if (nq < n_total) q_first = wq.seek(p, prefix, t_begin + nq);
+                        }
                     }
                 }
             }
@@ -426,6 +439,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 held[d] = nxt;
                 nxt = fetch_slot(d + 1);
             }
+            int nxt2 = fetch_slot(S + 1);                                 // page-table entries are read two units ahead of their use
             for (int j = 0; j < J; ++j) {
                 const int g = j / UPW, ku = j - g * UPW, k = xw + ku * C::XW, st = g % NS, buf = j % S;
                 cp_async_wait_pending<S - 1>();                           // this lane's copies of unit j have landed
@@ -446,32 +460,35 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     e = max(e, sc[i]);
                 }
                 __syncwarp();                                             // the buffer has been read by every lane
+                // the buffer goes back in flight at once: the copies of unit j + S (an empty group past the end)
+#pragma unroll
+                for (int it = 0; it < PER; ++it) issue_part(buf, nxt, it);
+                cp_async_commit();
+                if (S == 1 || buf == 0) held[0] = nxt; else held[S - 1] = nxt;
+                nxt = nxt2;
+                nxt2 = fetch_slot(j + S + 2);
                 const int e_unit = (int)__reduce_max_sync(0xffffffffu, e);
+                // The arithmetic needs no operand stage, so it is done (and pinned in registers) before the wait for the
+                // stage: only the stores are left on the path between "stage free" and "tile ready".
+                uint4 ob[2 * NBH];
+#pragma unroll
+                for (int i = 0; i < NBH; ++i) dequant_block(v[i], (int)sc[i] - e_unit + 6, ob[2 * i], ob[2 * i + 1]);
+#pragma unroll
+                for (int i = 0; i < 2 * NBH; ++i) asm volatile("" : "+r"(ob[i].x), "+r"(ob[i].y), "+r"(ob[i].z), "+r"(ob[i].w));
                 if (ku == 0) {
                     if (xw == 0 && lane == 0) TRACE(2, g);
                     mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);          // the operand stage is free
                     if (xw == 0 && lane == 0) TRACE(3, g);
                 }
                 if (lane == 0) ms.tile_exp[st][k] = e_unit;
-                // The arithmetic of unit j is interleaved with the copy instructions of unit j + S (an empty group past
-                // the end), which go into the buffer just read.
                 unsigned char* dst_lat = smem + st * STAGE_BYTES + k * (UNIT_TOK * 128);   // panels 0-3: 128-byte rows
                 unsigned char* dst_rope = smem + st * STAGE_BYTES + k * (UNIT_TOK * 64);   // rope panel: 64-byte rows
-                constexpr int IPT = (PER + NBH - 1) / NBH;                // copy instructions per block
 #pragma unroll
                 for (int i = 0; i < NBH; ++i) {
-#pragma unroll
-                    for (int q = 0; q < IPT; ++q)
-                        if (i * IPT + q < PER) issue_part(buf, nxt, i * IPT + q);
-                    uint4 a, b;
-                    dequant_block(v[i], (int)sc[i] - e_unit + 6, a, b);
                     unsigned char* d = (2 * (2 * i) >= 32 ? dst_rope : dst_lat) + st_off[i];   // block par + 2i >= 16: rope dims
-                    *reinterpret_cast<uint4*>(d) = a;
-                    *reinterpret_cast<uint4*>(reinterpret_cast<uintptr_t>(d) ^ 16) = b;
+                    *reinterpret_cast<uint4*>(d) = ob[2 * i];
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uintptr_t>(d) ^ 16) = ob[2 * i + 1];
                 }
-                cp_async_commit();
-                if (S == 1 || buf == 0) held[0] = nxt; else held[S - 1] = nxt;
-                nxt = fetch_slot(j + S + 1);
                 if (ku == UPW - 1) {
                     fence_proxy_async();                                  // the MMA reads the tile through the async proxy
                     mbar_arrive(&ms.kv_full[st]);
