@@ -316,3 +316,91 @@ def test_split_kv_decoder_buffers_on_gpu(pkg, impl):
     assert_close(merged, ref_o, tight=1.5e-2)
     assert torch.allclose(dec.local_lse().cpu(), ref_l, atol=2e-2)
     assert_close(dec.local_o(), ref_o, tight=1.5e-2)
+
+
+# ------------------------------------------------------------------------------------------------
+# block-scaled caches on the tcgen05 path: exponent frames, E8M0 row alignment, split bf16 Q
+# ------------------------------------------------------------------------------------------------
+
+def _scaled_mxfp4_case(pkg, lens, row_gain, seed, heads=16):
+    """An MXFP4 problem whose cache rows are multiplied by `row_gain[slot]` before quantisation."""
+    from amd_optimization_challenge_b200 import inputs
+    T = sum(lens)
+    g = torch.Generator().manual_seed(seed)
+    kv = torch.randn(T, 576, generator=g) * row_gain[:, None]
+    q = torch.randn(len(lens), heads, 576, generator=g).bfloat16()
+    codes, scales = inputs.quantize_mxfp4(kv.bfloat16())
+    ip = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    ip[1:] = torch.cumsum(torch.tensor(lens), 0)
+    return q, codes.reshape(T, 288), scales[:T, :18].contiguous(), ip
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("pattern", ["rising", "falling", "spiky", "tiny_unit"])
+def test_mxfp4_exponent_frames(pkg, impl, pattern):
+    """Row magnitudes spread over many binades, so that the 16-token units of a tile (and the tiles
+    of a sequence) get different exponent frames and O has to move to a larger frame mid-sequence."""
+    lens = [700, 130, 257]
+    T = sum(lens)
+    t = torch.arange(T, dtype=torch.float32)
+    if pattern == "rising":
+        gain = torch.exp2(-10 + 18 * t / T)                       # 2^-10 .. 2^8 along the cache
+    elif pattern == "falling":
+        gain = torch.exp2(8 - 18 * t / T)
+    elif pattern == "spiky":
+        gain = torch.where((t.long() % 97) == 0, torch.tensor(2.0 ** 7), torch.tensor(2.0 ** -6))
+    else:
+        gain = torch.where((t.long() // 16) % 5 == 2, torch.tensor(2.0 ** -20), torch.tensor(1.0))
+    q, codes, scales, ip = _scaled_mxfp4_case(pkg, lens, gain, seed=77)
+    sm = 576 ** -0.5
+    ref, _ = mo.mla_decode(q.float(), mo.dequant_kv("mxfp4", (codes, scales)), ip.numpy(), None, sm)
+    for max_ctas in (1, 3, 0):
+        out = pkg.mla_decode(q.cuda(), None, "mxfp4", (codes.cuda(), scales.cuda()), ip.cuda(), sm_scale=sm,
+                             impl=impl, max_ctas=max_ctas)
+        torch.cuda.synchronize()
+        assert_close(out, ref.bfloat16(), tight=1.5e-2)
+
+
+def test_mxfp4_scale_rows_at_any_even_offset(pkg):
+    """The E8M0 rows are fetched as aligned 8-byte words around each 18-byte row: every start
+    offset inside a word has to give the same result; an odd base address is not covered by the
+    tcgen05 kernel and is served by the generic one."""
+    lens = [300, 77]
+    T = sum(lens)
+    q, codes, scales, ip = _scaled_mxfp4_case(pkg, lens, torch.ones(T), seed=5)
+    sm = 576 ** -0.5
+    base = pkg.mla_decode(q.cuda(), None, "mxfp4", (codes.cuda(), scales.cuda()), ip.cuda(), sm_scale=sm, impl="generic")
+    for off in (0, 2, 4, 6, 8, 10):
+        buf = torch.zeros(T * 18 + 64, dtype=torch.uint8, device="cuda")
+        view = buf[off:off + T * 18].view(T, 18)
+        view.copy_(scales.cuda())
+        out = pkg.mla_decode(q.cuda(), None, "mxfp4", (codes.cuda(), view), ip.cuda(), sm_scale=sm, impl="tcgen05")
+        torch.cuda.synchronize()
+        assert_close(out, base, rtol=1e-2, atol=2e-3)
+    buf = torch.zeros(T * 18 + 64, dtype=torch.uint8, device="cuda")
+    odd = buf[1:1 + T * 18].view(T, 18)
+    odd.copy_(scales.cuda())
+    with pytest.raises(RuntimeError, match="status -2"):
+        pkg.mla_decode(q.cuda(), None, "mxfp4", (codes.cuda(), odd), ip.cuda(), sm_scale=sm, impl="tcgen05")
+    out = pkg.mla_decode(q.cuda(), None, "mxfp4", (codes.cuda(), odd), ip.cuda(), sm_scale=sm, impl="auto")
+    torch.cuda.synchronize()
+    assert_close(out, base, rtol=1e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("kv_format", ["fp8", "mxfp4", "hybrid"])
+def test_bf16_q_split_dynamic_range(pkg, kv_format):
+    """bf16 Q goes to the tensor cores as two e4m3 planes with one power-of-two scale per group of
+    query rows: heads whose magnitudes differ by 2^10, a zero head and a tiny sequence."""
+    lens = [260, 3, 129]
+    data = pkg.generate_input(len(lens), 1, max(lens), seed=91, kv_lens=lens, shuffle_pages=True, num_heads=32,
+                              formats=(kv_format,))
+    q = data[0].clone()
+    gains = torch.exp2(torch.linspace(-6, 4, 32)).to(q.device)
+    q = (q.float() * gains[None, :, None]).bfloat16()
+    q[:, 5] = 0
+    data = (q, data[1], data[2], data[3], data[4])
+    ref = oracle_for_data(data, kv_format, "bf16")
+    a = _run(pkg, data, kv_format, "bf16", "tcgen05")
+    b = _run(pkg, data, kv_format, "bf16", "generic")
+    assert_close(a, ref, tight=1.5e-2)
+    assert_close(b, ref, tight=1.5e-2)
