@@ -288,7 +288,9 @@ def main():
         out = call(rot[i % n_rot])
     barrier()
     graph = None
-    if not args.no_graph:
+    # the split-KV step contains an NCCL collective: it is launched eagerly (a captured collective has not been
+    # validated on this stack), every other mode replays a graph
+    if not args.no_graph and mode != "split_kv":
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -312,9 +314,19 @@ def main():
     # ---- clocks are sampled from before the pre-roll (same work, untimed) to after the timed region
     sampler = ClockSampler(local_rank)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # The pre-roll and the tail run a FIXED number of steps, the same on every rank (a time-based loop would let
+    # the ranks disagree on how many collectives they issue): sized from one probe batch, agreed by a MAX all-reduce.
+    t0 = time.perf_counter()
+    run_steps(8 * n_rot)
+    torch.cuda.synchronize()
+    probe = torch.tensor([time.perf_counter() - t0], device=dev)
+    if world > 1:
+        dist.all_reduce(probe, op=dist.ReduceOp.MAX)
+    batch_s = max(float(probe.item()), 1e-4)
+    pre_batches = max(1, min(2000, int(0.7 / batch_s)))
+    post_batches = max(1, min(700, int(0.25 / batch_s)))
     with sampler:
-        t_end = time.perf_counter() + 0.7
-        while time.perf_counter() < t_end:
+        for _ in range(pre_batches):
             run_steps(8 * n_rot)
             torch.cuda.synchronize()
         barrier()
@@ -323,8 +335,7 @@ def main():
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
-        t_end = time.perf_counter() + 0.25
-        while time.perf_counter() < t_end:
+        for _ in range(post_batches):
             run_steps(8 * n_rot)
             torch.cuda.synchronize()
     clocks = sampler.summary()
