@@ -13,6 +13,7 @@ size_t generic_smem_bytes(int batch);
 cudaError_t launch_sm100(const MlaParams& p, int* status, cudaStream_t stream);
 bool sm100_supported(const MlaParams& p);
 int sm100_rows_per_cta(const MlaParams& p);
+int sm100_tile_tokens(const MlaParams& p);
 cudaError_t launch_sm100x(const MlaParams& p, int* status, cudaStream_t stream);
 bool sm100x_supported(const MlaParams& p);
 int sm100x_rows_per_cta(const MlaParams& p);
@@ -144,7 +145,11 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     }
 
     int ctas_per_sm;
-    if (use_sm100) { p.tile_tokens = 128; p.rows_per_cta = plain ? sm100_rows_per_cta(p) : sm100x_rows_per_cta(p); ctas_per_sm = 1; }
+    if (use_sm100) {
+        p.tile_tokens = plain ? sm100_tile_tokens(p) : 128;
+        p.rows_per_cta = plain ? sm100_rows_per_cta(p) : sm100x_rows_per_cta(p);
+        ctas_per_sm = 1;
+    }
     else { p.tile_tokens = 64; p.rows_per_cta = 16; ctas_per_sm = 2; }
     const int groups = p.rows / p.rows_per_cta;
     long long hint = a->total_kv_hint > 0 ? a->total_kv_hint : a->num_slots;

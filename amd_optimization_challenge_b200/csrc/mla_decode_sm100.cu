@@ -36,11 +36,9 @@
 namespace b200mla {
 namespace sm100 {
 
-constexpr int TILE = 128;                 // tokens per tile = UMMA M
-constexpr int NS = 2;                     // cache tile stages
-constexpr int PANEL_BYTES = TILE * 128;   // one 128-byte-wide swizzled panel of a tile
-constexpr int NPANEL = 5;                 // 576 B per row = 4.5 panels (the last one half used)
-constexpr int STAGE_BYTES = NPANEL * PANEL_BYTES;
+constexpr int MMA_M = 128;                // rows of every MMA: tokens for QK, output dims for PV; S and P span MMA_M rows
+constexpr int NS_MAX = 3;
+constexpr int SMEM_LIMIT = 232448;        // opt-in shared memory per CTA
 constexpr float RECENTER = 4.0f;          // log2 units
 constexpr float P_SCALE_LOG2 = 4.0f;      // probabilities are stored multiplied by 2^4
 // Optional timeline instrumentation (compiled in only with -DB200MLA_TRACE; development aid).
@@ -54,15 +52,27 @@ __device__ long long* g_trace = nullptr;
 
 
 // ----------------------------------------------------------------------------------------------
+// N = 16: three stages of 112-token tiles (63 KB each).  Every MMA still spans 128 rows: rows 112..127 of a QK
+// operand are the first rows of whatever follows the panel (their scores are never read), and the phantom tokens
+// 112..127 of a PV k-step are the head of the next panel of the same stage, multiplied by probabilities that are
+// written as zeros.  The third stage is worth more than the 12.5 % of MMA rows it gives up: a stage is held from
+// the start of its gather until PV of its tile, about two tile periods of tensor work plus the gather latency.
+// N = 32: two stages of 128-token tiles (Q and P take the room of a third stage).
 template <int N>
 struct Layout {
+    static constexpr int TILE = (N == 16) ? 112 : 128;           // tokens per tile
+    static constexpr int NS = (N == 16) ? 3 : 2;                 // cache tile stages
+    static constexpr int PANEL_BYTES = TILE * 128;               // dims 128j..128j+127, 128B swizzle
+    static constexpr int ROPE_PANEL_BYTES = TILE * 64;           // dims 512..575: 64-byte rows, 64B swizzle
+    static constexpr int STAGE_BYTES = 4 * PANEL_BYTES + ROPE_PANEL_BYTES;
+    static constexpr int NPANEL = 5;                             // Q keeps five 128-byte-wide panels
     static constexpr int PRODUCER_WARPS = (N == 16) ? 11 : 2;    // 512 threads at 128 registers; N = 32 needs the registers
     static constexpr int PRODUCERS = 32 * PRODUCER_WARPS;
     static constexpr int THREADS = 160 + PRODUCERS;
     static constexpr int Q_PANEL_BYTES = N * 128;
     static constexpr int Q_BYTES = NPANEL * Q_PANEL_BYTES;        // one Q buffer (two of them: next sequence's Q loads early)
     static constexpr int P_CHUNKS = 2 * N / 16;                  // 16-column chunks of [hi | lo]
-    static constexpr int P_BUF_BYTES = P_CHUNKS * TILE * 16;
+    static constexpr int P_BUF_BYTES = P_CHUNKS * MMA_M * 16;
     static constexpr int OFF_Q = NS * STAGE_BYTES;
     static constexpr int OFF_P = OFF_Q + 2 * Q_BYTES;
     static constexpr int OFF_MISC = OFF_P + 2 * P_BUF_BYTES;
@@ -72,11 +82,11 @@ struct Layout {
 };
 
 struct Misc {
-    uint64_t kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], p_empty[2];
+    uint64_t kv_full[NS_MAX], kv_empty[NS_MAX], s_full[2], s_empty[2], p_full[2], p_empty[2];
     uint64_t q_full[2], q_empty[2], o_free;
     uint32_t tmem_base;
     int abort_flag;
-    int slot[NS][TILE];
+    int slot[NS_MAX][MMA_M];
     float red[4][32];            // cross-warp exchange (max / sum), 32 = max N
 };
 
@@ -84,6 +94,7 @@ template <int N>
 __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel(const MlaParams p, int* status) {
     using L = Layout<N>;
     constexpr int PRODUCERS = L::PRODUCERS, THREADS = L::THREADS;
+    constexpr int TILE = L::TILE, NS = L::NS, PANEL_BYTES = L::PANEL_BYTES, STAGE_BYTES = L::STAGE_BYTES;
     extern __shared__ __align__(1024) unsigned char smem[];
     Misc& ms = *reinterpret_cast<Misc*>(smem + L::OFF_MISC);
     int* prefix = reinterpret_cast<int*>(smem + L::OFF_MISC + sizeof(Misc));
@@ -169,20 +180,26 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 if (pt == 0) TRACE(0, g);
                 slots_for(g + 1);
                 const uint32_t stage_addr = smem_base + st * STAGE_BYTES;
-                for (int id0 = pt; id0 < TILE * 36; id0 += 8 * PRODUCERS) {   // batches of 8: slots first, then the copies
-                    int sl[8];
+                // Slots first, then the copies, if possible for the whole tile at once: a shared-memory load that sits
+                // between copy instructions waits behind them in the load/store unit, and the copies after it wait for
+                // the load (measured in isolation: 4.1 TB/s with two batches per tile, 5.4 TB/s with one).
+                constexpr int PER_TILE = (TILE * 36 + PRODUCERS - 1) / PRODUCERS;
+                constexpr int BATCH = PER_TILE < 16 ? PER_TILE : 16;
+                for (int id0 = pt; id0 < TILE * 36; id0 += BATCH * PRODUCERS) {
+                    int sl[BATCH];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
+                    for (int u = 0; u < BATCH; ++u) {
                         const int id = id0 + u * PRODUCERS;
                         sl[u] = id < TILE * 36 ? ms.slot[st][id / 36] : -2;
                     }
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
+                    for (int u = 0; u < BATCH; ++u) {
                         const int id = id0 + u * PRODUCERS;
                         if (sl[u] != -2) {
                             const int tok = id / 36, c = id - tok * 36;
                             const uint8_t* src = p.kv_codes + (long long)(sl[u] < 0 ? 0 : sl[u]) * p.kv_codes_stride + c * 16;
-                            const uint32_t dst = stage_addr + (c >> 3) * PANEL_BYTES + tok * 128 + (((c & 7) ^ (tok & 7)) << 4);
+                            const uint32_t dst = c < 32 ? stage_addr + (c >> 3) * PANEL_BYTES + tok * 128 + (((c & 7) ^ (tok & 7)) << 4)
+                                                        : stage_addr + 4 * PANEL_BYTES + tok * 64 + (((c - 32) ^ ((tok >> 1) & 3)) << 4);
                             cp_async16(dst, src, sl[u] < 0 ? 0u : 16u);     // rows past the end of the sequence: zero fill
                         }
                     }
@@ -194,13 +211,14 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
         } else if (warp == 4) {
             // =========================== MMA issue (one lane) ===========================
             if (lane == 0) {
-                constexpr uint32_t IDESC_QK = make_idesc(TILE, N, false, false);
+                constexpr uint32_t IDESC_QK = make_idesc(MMA_M, N, false, false);
                 constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
                 // descriptor bases; per-MMA descriptors differ only in the start address
                 const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                  // + stage
+                const uint64_t d_qk_a_rope = make_desc(smem_base + 4 * PANEL_BYTES, 16, 512, SWIZZLE_64B);   // + stage
                 const uint64_t d_qk_b = make_desc(smem_base + L::OFF_Q, 16, 1024, SWIZZLE_128B);       // + Q buffer
                 const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
-                const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, TILE * 16, SWIZZLE_NONE); // + buffer
+                const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, MMA_M * 16, SWIZZLE_NONE); // + buffer
                 Walker wq, wv;                                    // the QK stream runs ahead of the PV stream
                 wq.init(prefix, p.batch, t_begin);
                 wv = wq;
@@ -214,8 +232,12 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     const uint64_t b0 = desc_advance(d_qk_b, (wq.pair & 1) * L::Q_BYTES);
 #pragma unroll
                     for (int k = 0; k < 18; ++k) {
-                        umma_f8(tmem + L::TMEM_S + sb * N, desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32),
+                        const uint64_t a = k < 16 ? desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32)
+                                                  : desc_advance(d_qk_a_rope, st * STAGE_BYTES + (k & 1) * 32);
+#ifndef B200MLA_EXP_NO_QK
+                        umma_f8(tmem + L::TMEM_S + sb * N, a,
                                 desc_advance(b0, (k >> 2) * L::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
+#endif
                     }
                     umma_commit(&ms.s_full[sb]);
                     // last tile of this (CTA, sequence) pair: its Q buffer is free once these MMAs have run
@@ -233,8 +255,10 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     for (int j = 0; j < 4; ++j) {
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
+#ifndef B200MLA_EXP_NO_PV
                             umma_f8(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
                                     desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
+#endif
                         }
                     }
                     umma_commit(&ms.kv_empty[st]);
@@ -330,8 +354,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 mbar_arrive(&ms.s_empty[sb]);
 
                 // x = log2-domain exponent of the stored probability: score*scale - m_ref + P_SCALE_LOG2
-                const int pos = pos_first + tid;
-                const bool masked_tile = pos_first + TILE > lim_min;                 // uniform
+                const int pos = tid < TILE ? pos_first + tid : 0x7fffffff;           // lanes beyond the tile: always masked
+                const bool masked_tile = TILE < MMA_M || pos_first + TILE > lim_min; // uniform
                 float x[N];
 #pragma unroll
                 for (int c = 0; c < N; ++c) x[c] = fmaf(s[c], score_scale, nm[c]);
@@ -404,8 +428,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         lo[q4] = pack_e4m3x4((pv[0] - h01.x) * 16.0f, (pv[1] - h01.y) * 16.0f,
                                              (pv[2] - h23.x) * 16.0f, (pv[3] - h23.y) * 16.0f);
                     }
-                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (TILE * 16) + tid * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (TILE * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (MMA_M * 16) + tid * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (MMA_M * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
                 fence_proxy_async();
                 mbar_arrive(&ms.p_full[sb]);
@@ -473,11 +497,20 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
 
 }  // namespace sm100
 
-bool sm100_supported(const MlaParams& p) {
-    // the tile-prefix table shares the tail of shared memory with the rings: batch <= 4096
-    return p.kv_format == KV_E4M3 && p.q_format == Q_E4M3 && p.rows % 16 == 0 && p.batch <= 4096;
-}
 int sm100_rows_per_cta(const MlaParams& p) { return p.rows % 32 == 0 ? 32 : 16; }
+int sm100_tile_tokens(const MlaParams& p) { return sm100_rows_per_cta(p) == 32 ? sm100::Layout<32>::TILE : sm100::Layout<16>::TILE; }
+
+template <int N>
+static size_t smem_need(int batch) {
+    return (size_t)sm100::Layout<N>::OFF_MISC + sizeof(sm100::Misc) + (size_t)(batch + 1) * sizeof(int);
+}
+
+bool sm100_supported(const MlaParams& p) {
+    if (p.kv_format != KV_E4M3 || p.q_format != Q_E4M3 || p.rows % 16 != 0) return false;
+    // the tile-prefix table shares the tail of shared memory with the stages
+    const size_t need = sm100_rows_per_cta(p) == 32 ? smem_need<32>(p.batch) : smem_need<16>(p.batch);
+    return need <= (size_t)sm100::SMEM_LIMIT;
+}
 
 #ifdef B200MLA_TRACE
 extern "C" int b200_mla_debug_set_trace(long long* ptr) {
@@ -488,7 +521,7 @@ extern "C" int b200_mla_debug_set_trace(long long* ptr) {
 template <int N>
 static cudaError_t launch_n(const MlaParams& p, int* status, cudaStream_t stream) {
     using L = sm100::Layout<N>;
-    const size_t smem = (size_t)L::OFF_MISC + sizeof(sm100::Misc) + (size_t)(p.batch + 1) * sizeof(int);
+    const size_t smem = smem_need<N>(p.batch);
     cudaError_t e = cudaFuncSetAttribute(sm100::mla_decode_sm100_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     dim3 grid(p.num_ctas, p.rows / N);

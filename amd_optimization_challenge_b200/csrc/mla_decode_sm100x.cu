@@ -202,15 +202,15 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             // consecutive columns.  Rows past the end of the sequence are zero filled.
             auto gather = [&](int st, int tok0, int ntok, int ncols, const uint8_t* src_base, long long stride, auto dst_of) {
                 const int total = ntok * ncols;
-                for (int id0 = pt; id0 < total; id0 += 8 * PRODUCERS) {   // batches of 8: slots first, then the copies
-                    int sl[8];
+                for (int id0 = pt; id0 < total; id0 += 16 * PRODUCERS) {   // batches of 16: slots first, then the copies
+                    int sl[16];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
+                    for (int u = 0; u < 16; ++u) {
                         const int id = id0 + u * PRODUCERS;
                         sl[u] = id < total ? ms.slot[st][tok0 + id / ncols] : -2;
                     }
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
+                    for (int u = 0; u < 16; ++u) {
                         const int id = id0 + u * PRODUCERS;
                         if (sl[u] != -2) {
                             const int tr = id / ncols, c = id - tr * ncols;
