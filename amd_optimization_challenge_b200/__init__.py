@@ -16,7 +16,7 @@ imported before the library exists); if libb200mla.so has not been built, that a
 from .inputs import (generate_input, quantize_fp8, quantize_mxfp4, dequantize_mxfp4, quantize_hybrid,
                      QK_HEAD_DIM, V_HEAD_DIM, KV_LORA_RANK, QK_ROPE_HEAD_DIM)
 
-_LIB_BACKED = ("custom_kernel", "mla_decode", "combine_partials", "quantize_q_fp8")
+_LIB_BACKED = ("custom_kernel", "mla_decode", "combine_partials", "quantize_q_fp8", "q_amax_parts", "q_amax_parts")
 
 
 def __getattr__(name):
@@ -28,7 +28,7 @@ def __getattr__(name):
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 __all__ = [
-    "custom_kernel", "mla_decode", "combine_partials", "quantize_q_fp8",
+    "custom_kernel", "mla_decode", "combine_partials", "quantize_q_fp8", "q_amax_parts",
     "generate_input", "quantize_fp8", "quantize_mxfp4", "dequantize_mxfp4", "quantize_hybrid",
     "QK_HEAD_DIM", "V_HEAD_DIM", "KV_LORA_RANK", "QK_ROPE_HEAD_DIM",
 ]

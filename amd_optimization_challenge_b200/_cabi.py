@@ -11,7 +11,8 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libb200mla.so")
 
-Q_BF16, Q_E4M3 = 0, 1
+Q_BF16, Q_E4M3, Q_BF16_CAST_E4M3 = 0, 1, 2
+Q_AMAX_PARTS = 256
 KV_E4M3, KV_MXFP4, KV_HYBRID = 0, 1, 2
 IMPL_AUTO, IMPL_GENERIC, IMPL_TCGEN05 = 0, 1, 2
 
@@ -36,7 +37,8 @@ class DecodeArgs(ctypes.Structure):
 
 
 EXPORTS = ("b200_mla_version", "b200_mla_last_error", "b200_mla_workspace_bytes", "b200_mla_decode",
-           "b200_mla_combine", "b200_mla_quantize_fp8", "b200_mla_set_stage1_events", "b200_mla_decode_static")
+           "b200_mla_combine", "b200_mla_quantize_fp8", "b200_mla_q_amax", "b200_mla_set_stage1_events",
+           "b200_mla_decode_static")
 
 
 def _load() -> ctypes.CDLL:
@@ -55,6 +57,8 @@ def _load() -> ctypes.CDLL:
     lib.b200_mla_combine.argtypes = [_vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp]
     lib.b200_mla_quantize_fp8.restype = _i32
     lib.b200_mla_quantize_fp8.argtypes = [_vp, _i64, _vp, _vp, _vp, _vp]
+    lib.b200_mla_q_amax.restype = _i32
+    lib.b200_mla_q_amax.argtypes = [_vp, _i64, _vp, _vp]
     lib.b200_mla_decode_static.restype = _i32
     lib.b200_mla_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), _vp]
     lib.b200_mla_set_stage1_events.restype = _i32

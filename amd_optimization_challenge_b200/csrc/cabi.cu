@@ -25,6 +25,7 @@ cudaError_t launch_combine_parts(const float* o_parts, const float* lse_parts, i
                                  cudaStream_t stream);
 cudaError_t launch_quantize_fp8(const __nv_bfloat16* x, long long n, uint8_t* out, float* scale_out,
                                 unsigned int* scratch, cudaStream_t stream);
+cudaError_t launch_q_amax_parts(const __nv_bfloat16* x, long long n, unsigned int* parts, cudaStream_t stream);
 }  // namespace b200mla
 
 using namespace b200mla;
@@ -95,12 +96,13 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     if (a->batch > MAX_BATCH) return fail(B200_MLA_ERR_TOO_LARGE, "batch %d exceeds %d", a->batch, MAX_BATCH);
     if (a->heads % 16 != 0) return fail(B200_MLA_ERR_UNSUPPORTED, "heads must be a multiple of 16 (got %d)", a->heads);
     if (a->q_len > 8) return fail(B200_MLA_ERR_UNSUPPORTED, "q_len > 8 is not a decode shape (got %d)", a->q_len);
-    if (a->q_format != B200_MLA_Q_BF16 && a->q_format != B200_MLA_Q_E4M3)
+    if (a->q_format < B200_MLA_Q_BF16 || a->q_format > B200_MLA_Q_BF16_CAST_E4M3)
         return fail(B200_MLA_ERR_INVALID_ARG, "bad q_format %d", a->q_format);
     if (a->kv_format < B200_MLA_KV_E4M3 || a->kv_format > B200_MLA_KV_HYBRID)
         return fail(B200_MLA_ERR_INVALID_ARG, "bad kv_format %d", a->kv_format);
     if (!a->q || !a->kv_codes || !a->kv_indptr) return fail(B200_MLA_ERR_INVALID_ARG, "q, kv_codes and kv_indptr are required");
-    if (a->q_format == B200_MLA_Q_E4M3 && !a->q_scale) return fail(B200_MLA_ERR_INVALID_ARG, "q_scale is required for e4m3 Q");
+    if (a->q_format != B200_MLA_Q_BF16 && !a->q_scale)
+        return fail(B200_MLA_ERR_INVALID_ARG, "q_scale is required for e4m3 Q (the scale, or the amax partials when Q is cast on load)");
     if ((a->kv_format == B200_MLA_KV_E4M3 || a->kv_format == B200_MLA_KV_HYBRID) && !a->kv_scale)
         return fail(B200_MLA_ERR_INVALID_ARG, "kv_scale is required for e4m3 / hybrid caches");
     if (a->kv_format != B200_MLA_KV_E4M3 && !a->kv_block_scales)
@@ -120,9 +122,12 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     MlaParams p;
     memset(&p, 0, sizeof(p));
     p.batch = a->batch; p.heads = a->heads; p.q_len = a->q_len; p.rows = a->heads * a->q_len;
-    p.q_format = a->q_format; p.kv_format = a->kv_format; p.causal = a->causal ? 1 : 0; p.page_size = a->page_size;
+    // bf16 Q cast on load: for every kernel that is an e4m3 Q whose bytes are made while they are loaded
+    p.q_cast = a->q_format == B200_MLA_Q_BF16_CAST_E4M3 ? 1 : 0;
+    p.q_amax_parts = p.q_cast ? reinterpret_cast<const unsigned int*>(a->q_scale) : nullptr;
+    p.q_format = p.q_cast ? (int)Q_E4M3 : a->q_format; p.kv_format = a->kv_format; p.causal = a->causal ? 1 : 0; p.page_size = a->page_size;
     p.sm_scale = a->sm_scale;
-    p.q = a->q; p.q_row_stride = a->q_row_stride; p.q_head_stride = a->q_head_stride; p.q_scale = a->q_scale;
+    p.q = a->q; p.q_row_stride = a->q_row_stride; p.q_head_stride = a->q_head_stride; p.q_scale = p.q_cast ? nullptr : a->q_scale;
     p.kv_codes = (const uint8_t*)a->kv_codes; p.kv_codes_stride = a->kv_codes_stride;
     p.kv_bs = (const uint8_t*)a->kv_block_scales; p.kv_bs_stride = a->kv_block_scales_stride;
     p.kv_rope = (const uint8_t*)a->kv_rope; p.kv_rope_stride = a->kv_rope_stride;
@@ -239,6 +244,16 @@ int32_t b200_mla_combine(const float* o_parts, const float* lse_parts, int32_t p
     cudaError_t e = launch_combine_parts(o_parts, lse_parts, parts, rows, o_part_stride, lse_part_stride,
                                         (__nv_bfloat16*)out, out_lse, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_q_amax(const void* x_bf16, int64_t n, uint32_t* parts_out, void* stream) {
+    if (!x_bf16 || !parts_out) return fail(B200_MLA_ERR_INVALID_ARG, "NULL argument");
+    if (n <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "n must be positive");
+    if (((uintptr_t)x_bf16 & 15) || ((uintptr_t)parts_out & 3))
+        return fail(B200_MLA_ERR_INVALID_ARG, "x must be 16-byte and parts_out 4-byte aligned");
+    cudaError_t e = launch_q_amax_parts((const __nv_bfloat16*)x_bf16, n, parts_out, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "amax launch failed: %s", cudaGetErrorString(e));
     return B200_MLA_OK;
 }
 

@@ -20,6 +20,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
 enum { Q_BF16 = 0, Q_E4M3 = 1 };
+constexpr int Q_AMAX_PARTS = 256;      // partial maxima handed over by the amax kernel when Q is cast on load
 enum { KV_E4M3 = 0, KV_MXFP4 = 1, KV_HYBRID = 2 };
 
 struct MlaParams {
@@ -44,6 +45,8 @@ struct MlaParams {
     int* tile_prefix;                   // [batch + 1] exclusive prefix of tiles per sequence
     uint8_t* q_split;                   // bf16 Q as two e4m3 planes [2][batch * rows][576] (tcgen05 kernels)
     float* q_split_scale;               // [batch][rows / rows_per_cta] factor that undoes the planes' scaling
+    int q_cast;                         // q is bf16 and is quantised to e4m3 (per-tensor, reference rule) as it is loaded;
+    const unsigned int* q_amax_parts;   //   its scale comes from these Q_AMAX_PARTS partial maxima (bf16 bit patterns)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -136,6 +139,44 @@ struct Walker {
         return true;
     }
 };
+
+// ---------------------------------------------------------------------------------------------
+// Per-tensor e4m3 quantisation of Q, arithmetic order of the reference's quantize_fp8
+// (competitor_submissions/mi355x_reference/reference.py:65-80): every intermediate is a bf16 value.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float q_scale_from_amax_bits(unsigned int bits) {
+    float amax = __bfloat162float(__ushort_as_bfloat16((unsigned short)bits));
+    amax = __bfloat162float(__float2bfloat16_rn(fmaxf(amax, 1e-12f)));
+    return __bfloat162float(__float2bfloat16_rn(amax / 448.0f));
+}
+__device__ __forceinline__ uint8_t q_cast_e4m3(__nv_bfloat16 x, float scale) {
+    float y = __bfloat162float(x) / scale;                                   // IEEE division
+    y = __bfloat162float(__float2bfloat16_rn(y));                            // bf16 rounding of the quotient
+    y = fminf(fmaxf(y, -448.0f), 448.0f);
+    return (uint8_t)__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
+}
+// eight bf16 values (one 16-byte vector) -> eight e4m3 bytes
+__device__ __forceinline__ uint2 q_cast_e4m3x8(const uint4& v, float scale) {
+    const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(&v);
+    uint32_t o[2] = {0u, 0u};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k >> 2] |= (uint32_t)q_cast_e4m3(in[k], scale) << (8 * (k & 3));
+    return make_uint2(o[0], o[1]);
+}
+// Scale of the e4m3 Q codes, the same value in every thread of the block.  All threads call it (it
+// synchronises the block when the scale has to be reduced from the partial maxima); `word` is one
+// 32-bit word of shared memory.
+__device__ inline float block_q_scale(const unsigned int* amax_parts, const float* q_scale, int q_cast, unsigned int* word) {
+    if (!q_cast) return q_scale ? __ldg(q_scale) : 1.0f;
+    if (threadIdx.x == 0) *word = 0u;
+    __syncthreads();
+    unsigned int m = 0;
+    for (int i = threadIdx.x; i < Q_AMAX_PARTS; i += blockDim.x) m = max(m, __ldg(amax_parts + i));
+    m = __reduce_max_sync(0xffffffffu, m);
+    if ((threadIdx.x & 31) == 0 && m) atomicMax(word, m);
+    __syncthreads();
+    return q_scale_from_amax_bits(*word);
+}
 
 // ---------------------------------------------------------------------------------------------
 // byte formats

@@ -33,6 +33,7 @@ struct Smem {
     float s_part[2 * ROWS * TILE];    // two K-halves of S; reused as per-warp 16x16 scratch
     __nv_bfloat16 ps[ROWS * PP];
     float m[ROWS], l[ROWS], alpha[ROWS];
+    unsigned int q_amax;               // block_q_scale's word
 };
 
 template <int KVFMT>
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(THREADS, 2) mla_decode_generic_kernel(const Ml
     if (t_begin >= t_end) return;
 
     // scalar scales: scores get q_scale * kv_scale(e4m3 cache) * sm_scale * log2e, outputs kv_scale
-    const float q_sc = p.q_format == Q_E4M3 ? __ldg(p.q_scale) : 1.0f;
+    const float q_sc = p.q_format == Q_E4M3 ? block_q_scale(p.q_amax_parts, p.q_scale, p.q_cast, &s.q_amax) : 1.0f;
     const float kv_sc = (KVFMT == KV_E4M3 || KVFMT == KV_HYBRID) ? __ldg(p.kv_scale) : 1.0f;
     const float score_scale = p.sm_scale * LOG2E * q_sc * (KVFMT == KV_E4M3 ? kv_sc : 1.0f);
     const float out_scale = KVFMT == KV_E4M3 ? kv_sc : 1.0f;
@@ -180,7 +181,13 @@ __global__ void __launch_bounds__(THREADS, 2) mla_decode_generic_kernel(const Ml
             long long off = (long long)(b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c8;
             __align__(16) __nv_bfloat16 o[8];
             const float f = (c8 >= V_DIM) ? rope_q_scale : 1.0f;
-            if (p.q_format == Q_BF16) {
+            if (p.q_cast) {                      // bf16 in memory, used as the e4m3 value the reference's quantiser gives it
+                uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + off));
+                const uint2 codes = q_cast_e4m3x8(raw, q_sc);
+                const uint8_t* in = reinterpret_cast<const uint8_t*>(&codes);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = __float2bfloat16_rn(e4m3_to_float(in[k]) * f);
+            } else if (p.q_format == Q_BF16) {
                 uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + off));
                 const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll

@@ -86,6 +86,7 @@ struct Misc {
     uint64_t q_full[2], q_empty[2], o_free;
     uint32_t tmem_base;
     int abort_flag;
+    unsigned int q_amax;         // block_q_scale's word
     int slot[NS_MAX][MMA_M];
     float red[4][32];            // cross-warp exchange (max / sum), 32 = max N
 };
@@ -128,7 +129,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
     const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
 
-    const float q_sc = __ldg(p.q_scale), kv_sc = __ldg(p.kv_scale);
+    const float q_sc = block_q_scale(p.q_amax_parts, p.q_scale, p.q_cast, &ms.q_amax), kv_sc = __ldg(p.kv_scale);
     const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
     const float out_scale = kv_sc;
     volatile int* abort_flag = &ms.abort_flag;
@@ -163,14 +164,29 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     const int qb = wk.pair & 1;
                     mbar_wait(&ms.q_empty[qb], wk.pair / 2 - 1, abort_flag);
                     const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
-                    for (int i = pt; i < N * 36; i += PRODUCERS) {
-                        const int r = i / 36, c = i - r * 36;
-                        const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
-                                             (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
-                        cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
+                    if (p.q_cast) {
+                        // bf16 rows, quantised here: eight values in, eight e4m3 bytes (half a 16-byte column) out
+                        unsigned char* q_smem = smem + L::OFF_Q + qb * L::Q_BYTES;
+                        for (int i = pt; i < N * 72; i += PRODUCERS) {
+                            const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
+                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                                                       (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8;
+                            const uint2 o = q_cast_e4m3x8(__ldg(reinterpret_cast<const uint4*>(src)), q_sc);
+                            *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) = o;
+                        }
+                        fence_proxy_async();                      // the MMA reads Q through the async proxy
+                        mbar_arrive(&ms.q_full[qb]);
+                    } else {
+                        for (int i = pt; i < N * 36; i += PRODUCERS) {
+                            const int r = i / 36, c = i - r * 36;
+                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
+                                                 (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
+                            cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
+                        }
+                        cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
                     }
-                    cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
                 }
                 mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
 #pragma unroll

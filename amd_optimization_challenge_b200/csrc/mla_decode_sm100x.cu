@@ -94,6 +94,7 @@ struct Misc {
     uint64_t q_full, q_empty, o_free;
     uint32_t tmem_base;
     int abort_flag;
+    unsigned int q_amax;         // block_q_scale's word
     int tile_exp[NS][TILE / UNIT_TOK];   // exponent frame of each 16-token unit of the tile in each operand stage
     int slot[NS][TILE];
     float red[4][32];            // softmax cross-warp exchange
@@ -177,6 +178,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
 
     const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
     const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
+    const float q_tensor_scale = QFMT == Q_E4M3 ? block_q_scale(p.q_amax_parts, p.q_scale, p.q_cast, &ms.q_amax) : 1.0f;
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
@@ -258,6 +260,22 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     mbar_wait(&ms.q_empty, wk.pair - 1, abort_flag);
                     const uint32_t q_addr = smem_base + C::OFF_Q;
                     const long long plane = (long long)p.batch * p.rows * QK_DIM;   // split Q: hi plane, then lo plane
+                    if (!C::QSPLIT && p.q_cast) {
+                        // bf16 rows, quantised here: eight values in, eight e4m3 bytes (half a 16-byte column) out
+                        unsigned char* q_smem = smem + C::OFF_Q;
+                        for (int i = pt; i < N * 72; i += PRODUCERS) {
+                            const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
+                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                                                       (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8;
+                            const uint2 o = q_cast_e4m3x8(__ldg(reinterpret_cast<const uint4*>(src)), q_tensor_scale);
+                            const int off = c < 32 ? (c >> 3) * C::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)
+                                                   : 4 * C::Q_PANEL_BYTES + r * 64 + (((c - 32) ^ ((r >> 1) & 3)) << 4);
+                            *reinterpret_cast<uint2*>(q_smem + off + (v8 & 1) * 8) = o;
+                        }
+                        fence_proxy_async();                      // the MMA reads Q through the async proxy
+                        mbar_arrive(&ms.q_full);
+                    } else {
                     for (int i = pt; i < NQ * 36; i += PRODUCERS) {
                         const int r = i / 36, c = i - r * 36;
                         const uint8_t* src;
@@ -274,6 +292,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                         cp_async16(dst, src, 16u);
                     }
                     cp_async_mbar_arrive_noinc(&ms.q_full);
+                    }
                 }
             }
             cp_async_wait_all();
@@ -500,7 +519,6 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             // =========================== softmax / correction / epilogue (128 threads) ===========
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
             Walker wk; wk.init(prefix, p.batch, t_begin);
-            const float q_tensor_scale = QFMT == Q_E4M3 ? __ldg(p.q_scale) : 1.0f;
             const float kv_tensor_scale = KVFMT != KV_MXFP4 ? __ldg(p.kv_scale) : 1.0f;
             float qk_base = 0.0f;          // sm_scale * log2(e) * (scale of this sequence's Q bytes)
             int e_run = 0;                 // exponent frame of O (block-scaled caches)

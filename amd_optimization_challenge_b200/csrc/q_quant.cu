@@ -59,7 +59,40 @@ __global__ void cast_kernel(const __nv_bfloat16* __restrict__ x, long long n, ui
     }
 }
 
+// Per-block maxima of the bf16 magnitudes, Q_AMAX_PARTS blocks, every block writes its word.
+__global__ void __launch_bounds__(256) amax_parts_kernel(const __nv_bfloat16* __restrict__ x, long long n, unsigned int* parts) {
+    __shared__ unsigned int red[8];
+    unsigned int m = 0;
+    const long long stride = (long long)gridDim.x * blockDim.x * 8;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+        if (i + 8 <= n) {
+            uint4 v = __ldg(reinterpret_cast<const uint4*>(x + i));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                m = max(m, w[k] & 0x7fffu);
+                m = max(m, (w[k] >> 16) & 0x7fffu);
+            }
+        } else {
+            for (long long j = i; j < n; ++j) m = max(m, (unsigned)(__bfloat16_as_ushort(x[j]) & 0x7fffu));
+        }
+    }
+    m = __reduce_max_sync(0xffffffffu, m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 1; i < 8; ++i) m = max(m, red[i]);
+        parts[blockIdx.x] = m;
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_q_amax_parts(const __nv_bfloat16* x, long long n, unsigned int* parts, cudaStream_t stream) {
+    amax_parts_kernel<<<Q_AMAX_PARTS, 256, 0, stream>>>(x, n, parts);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_quantize_fp8(const __nv_bfloat16* x, long long n, uint8_t* out, float* scale_out,
                                 unsigned int* scratch, cudaStream_t stream) {

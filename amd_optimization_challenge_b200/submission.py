@@ -81,13 +81,32 @@ def quantize_q_fp8(q: torch.Tensor):
     return codes.view(torch.float8_e4m3fn), scale
 
 
+def q_amax_parts(q: torch.Tensor) -> torch.Tensor:
+    """First half of quantize_q_fp8: the partial maxima (uint32[256]) from which a decode call with
+    `q_cast=True` derives the per-tensor e4m3 scale of a bf16 Q.  The buffer is cached per shape."""
+    if not q.is_cuda or q.dtype != torch.bfloat16:
+        raise ValueError("q_amax_parts expects a CUDA bf16 tensor")
+    if not q.is_contiguous():
+        raise ValueError("q_amax_parts expects a contiguous tensor")
+    key = (q.device.index, tuple(q.shape), "amax")
+    parts = _qbuf_cache.get(key)
+    if parts is None:
+        parts = torch.empty(_cabi.Q_AMAX_PARTS, dtype=torch.int32, device=q.device)
+        _qbuf_cache[key] = parts
+    with torch.cuda.device(q.device):
+        check(lib.b200_mla_q_amax(q.data_ptr(), q.numel(), parts.data_ptr(), _stream(q.device)), "b200_mla_q_amax")
+    return parts
+
+
 def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Tensor, *, sm_scale: float,
                q_len: int = 1, kv_indices=None, page_size: int = 1, kv_page_indptr=None, causal: bool = True,
                total_kv_hint: int = 0, kv_pos_offset=None, kv_total_len=None, return_partial: bool = False,
-               impl: str = "auto", max_ctas: int = 0, partial_out=None):
+               impl: str = "auto", max_ctas: int = 0, partial_out=None, q_cast: bool = False):
     """One decode call through b200_mla_decode.
 
-    q         [batch*q_len, heads, 576] bf16, or float8_e4m3fn/uint8 codes with `q_scale` (f32[1])
+    q         [batch*q_len, heads, 576] bf16, or float8_e4m3fn/uint8 codes with `q_scale` (f32[1]);
+              with q_cast=True a bf16 q is quantised to e4m3 (per tensor, the reference's rule) while the
+              kernel loads it, and `q_scale` is the uint32[256] buffer of q_amax_parts(q)
     kv        "fp8": (codes [T,(1,)576], scale f32[1]); "mxfp4": (codes [T,(1,)288], E8M0 [>=T, >=18]);
               "hybrid": (latent codes [T,(1,)256], latent E8M0 [T,>=16], rope codes [T,(1,)64], rope scale f32[1])
     returns   bf16 O [batch*q_len, heads, 512]; with return_partial=True instead
@@ -107,7 +126,12 @@ def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Te
     a.causal, a.page_size, a.impl = int(causal), page_size, _IMPLS[impl]
     a.sm_scale = float(sm_scale)
     a.max_ctas = int(max_ctas)
-    if q.dtype == torch.bfloat16:
+    if q.dtype == torch.bfloat16 and q_cast:
+        if q_scale is None:
+            raise ValueError("q_cast needs the partial maxima of q_amax_parts(q) as q_scale")
+        a.q_format = _cabi.Q_BF16_CAST_E4M3
+        a.q_scale = q_scale.data_ptr()
+    elif q.dtype == torch.bfloat16:
         a.q_format = _cabi.Q_BF16
     elif q.dtype in (torch.float8_e4m3fn, torch.uint8):
         a.q_format = _cabi.Q_E4M3
@@ -207,9 +231,12 @@ def custom_kernel(data):
         raise KeyError(f"kv_data has no '{kv_format}' cache")
     q_format = config.get("q_format", "bf16" if kv_format == "mxfp4" else "fp8")
     q_len = int(config.get("q_seq_len", 1))
-    q_scale = None
+    q_scale, q_cast = None, False
     if q.dtype == torch.bfloat16 and q_format == "fp8":
-        q, q_scale = quantize_q_fp8(q)
+        # the reference quantises Q per tensor before its FP8 kernels (reference.py:65-80, 308-310); here only the
+        # amax is a launch of its own, the cast happens where the decode kernel loads Q
+        q = q.contiguous()
+        q_scale, q_cast = q_amax_parts(q), True
     elif q.dtype != torch.bfloat16:
         q_scale = config["q_scale"]
     if "total_kv" in config:
@@ -223,4 +250,4 @@ def custom_kernel(data):
         sm_scale=config["sm_scale"], q_len=q_len, kv_indices=config.get("kv_indices"),
         page_size=int(config.get("page_size", 1)), kv_page_indptr=config.get("kv_page_indptr"),
         causal=bool(config.get("causal", True)), total_kv_hint=hint, impl=config.get("impl", "auto"),
-        max_ctas=int(config.get("max_ctas", 0)))
+        max_ctas=int(config.get("max_ctas", 0)), q_cast=q_cast)

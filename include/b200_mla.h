@@ -31,7 +31,11 @@ typedef enum {
     B200_MLA_ERR_TOO_LARGE = -5         /* size beyond a documented limit */
 } b200_mla_status;
 
-typedef enum { B200_MLA_Q_BF16 = 0, B200_MLA_Q_E4M3 = 1 } b200_mla_q_format;
+/* B200_MLA_Q_BF16_CAST_E4M3: q is bf16 and is quantised to e4m3 with the reference's per-tensor rule while the
+ * decode kernel loads it (same codes and scale as b200_mla_quantize_fp8 followed by B200_MLA_Q_E4M3, one launch
+ * less); q_scale then points to the B200_MLA_Q_AMAX_PARTS partial maxima written by b200_mla_q_amax. */
+typedef enum { B200_MLA_Q_BF16 = 0, B200_MLA_Q_E4M3 = 1, B200_MLA_Q_BF16_CAST_E4M3 = 2 } b200_mla_q_format;
+#define B200_MLA_Q_AMAX_PARTS 256
 
 typedef enum {
     B200_MLA_KV_E4M3 = 0,    /* [slots, 576] e4m3fn codes + fp32 per-tensor scale            */
@@ -72,7 +76,8 @@ typedef struct {
     const void *q;            /* device; bf16 or e4m3fn */
     int64_t q_row_stride;     /* elements between consecutive query rows (heads*576 when dense) */
     int64_t q_head_stride;    /* elements between heads (576 when dense) */
-    const float *q_scale;     /* device fp32[1]; required for B200_MLA_Q_E4M3, else NULL */
+    const float *q_scale;     /* device fp32[1] for B200_MLA_Q_E4M3; the partial maxima (uint32[B200_MLA_Q_AMAX_PARTS])
+                               * of b200_mla_q_amax for B200_MLA_Q_BF16_CAST_E4M3; else NULL */
 
     /* ---- KV cache planes (device) ---- */
     const void *kv_codes;     /* e4m3: [slots,576]; mxfp4: [slots,288]; hybrid: latent [slots,256] */
@@ -153,6 +158,14 @@ int32_t b200_mla_combine(const float *o_parts, const float *lse_parts, int32_t p
  */
 int32_t b200_mla_quantize_fp8(const void *x_bf16, int64_t n, void *codes_out, float *scale_out,
                               void *scratch, void *stream);
+
+/*
+ * First half of that quantisation on its own (the amax of mixed-mla/fused_fp8_quant.py:27-53): the
+ * largest bf16 magnitude of x, left as B200_MLA_Q_AMAX_PARTS per-block partial maxima (bf16 bit
+ * patterns, uint32 each) in `parts_out`.  A decode call with q_format B200_MLA_Q_BF16_CAST_E4M3
+ * takes them through q_scale and does the cast itself.  One launch, no memset, no atomics.
+ */
+int32_t b200_mla_q_amax(const void *x_bf16, int64_t n, uint32_t *parts_out, void *stream);
 
 /*
  * Decode without any allocation on the caller's side (no counterpart in the reference, whose

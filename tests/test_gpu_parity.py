@@ -404,3 +404,21 @@ def test_bf16_q_split_dynamic_range(pkg, kv_format):
     b = _run(pkg, data, kv_format, "bf16", "generic")
     assert_close(a, ref, tight=1.5e-2)
     assert_close(b, ref, tight=1.5e-2)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("kv_format", ["fp8", "hybrid", "mxfp4"])
+def test_q_cast_on_load_equals_two_step_quantisation(pkg, impl, kv_format):
+    """custom_kernel quantises a bf16 Q for the FP8-Q paths inside the decode kernel (amax launch + cast on
+    load); the result has to be bit-identical to quantize_q_fp8 followed by a decode of the e4m3 codes."""
+    lens = [300, 1, 129, 0, 700]
+    for heads, q_len in ((16, 1), (32, 2)):
+        data = pkg.generate_input(len(lens), q_len, max(lens), seed=7 + heads, kv_lens=lens, shuffle_pages=True,
+                                  num_heads=heads, formats=(kv_format,))
+        q, kvd, _, ip, cfg = data
+        common = dict(sm_scale=cfg["sm_scale"], q_len=q_len, kv_indices=cfg["kv_indices"], impl=impl, max_ctas=3)
+        q8, sc = pkg.quantize_q_fp8(q)
+        two_step = pkg.mla_decode(q8, sc, kv_format, kvd[kv_format], ip, **common)
+        fused = pkg.mla_decode(q, pkg.q_amax_parts(q), kv_format, kvd[kv_format], ip, q_cast=True, **common)
+        torch.cuda.synchronize()
+        assert torch.equal(two_step, fused)
