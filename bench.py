@@ -415,7 +415,8 @@ def main():
                "sample": f"median of {args.cpu_reps} full {args.workload} calls ({t_cpu * 1e3:.1f} ms each)",
                "us_per_call": t_cpu * 1e6}
 
-    launches_per_step = 2 + (2 if w["q_format"] == "fp8" else 0)     # [amax, cast,] stage 1, combine
+    # stage 1 + combine, plus the amax of an FP8-cast Q or the e4m3 split of a bf16 Q (tcgen05 kernels only)
+    launches_per_step = 2 + (1 if (w["q_format"] == "fp8" or args.kernel != "generic") else 0)
     if mode == "split_kv":
         launches_per_step += 1                                        # merge of the gathered partials
     per_gpu = {"replica": "each rank decodes its own batch, no collective",
