@@ -250,10 +250,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     for (int k = 0; k < 18; ++k) {
                         const uint64_t a = k < 16 ? desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32)
                                                   : desc_advance(d_qk_a_rope, st * STAGE_BYTES + (k & 1) * 32);
-#ifndef B200MLA_EXP_NO_QK
                         umma_f8(tmem + L::TMEM_S + sb * N, a,
                                 desc_advance(b0, (k >> 2) * L::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
-#endif
                     }
                     umma_commit(&ms.s_full[sb]);
                     // last tile of this (CTA, sequence) pair: its Q buffer is free once these MMAs have run
@@ -271,10 +269,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     for (int j = 0; j < 4; ++j) {
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
-#ifndef B200MLA_EXP_NO_PV
                             umma_f8(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
                                     desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
-#endif
                         }
                     }
                     umma_commit(&ms.kv_empty[st]);
