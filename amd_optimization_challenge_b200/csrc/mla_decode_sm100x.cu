@@ -3,10 +3,10 @@
 // become e4m3 operands) and bf16 queries (split into two e4m3 terms).  Same swap-AB formulation,
 // schedule, softmax and pipeline as mla_decode_sm100.cu (FP8 Q x FP8 KV), plus:
 //
-//  * "transform" warps between the gather and the MMA.  For a block-scaled cache the gather lands
-//    the raw codes and E8M0 bytes of 16 tokens at a time (a unit) in a ring; a transform warp turns
-//    every 32-code block of a unit into 32 e4m3 bytes of the swizzled operand tile.  All blocks of a
-//    unit share one exponent frame: byte value = e2m1 * 2^(scale - E_unit + 6) with E_unit the largest
+//  * "transform" warps.  For a block-scaled cache each transform warp fetches the raw codes and E8M0
+//    bytes of 16 tokens at a time (a unit) into a landing buffer of its own, and turns every 32-code
+//    block of a landed unit into 32 e4m3 bytes of the swizzled operand tile.  All blocks of a unit
+//    share one exponent frame: byte value = e2m1 * 2^(scale - E_unit + 6) with E_unit the largest
 //    E8M0 byte of the unit, which is exact in e4m3 for blocks up to 14 binades below the largest.
 //    The softmax thread of a token applies 2^(E_unit - 133) to its scores and 2^(E_unit - E_run) to
 //    its probabilities, E_run being the frame O is held in (O is rescaled in TMEM when a later tile
@@ -20,7 +20,8 @@
 //
 // Operand tile: four 128-byte-wide panels (dims 0..511, 128B swizzle; read K-major by QK and MN-major
 // by PV) and one 64-byte-wide panel (dims 512..575, 64B swizzle; QK only).
-// Roles: warps 0-3 softmax / epilogue, warp 4 MMA issue, then PW gather warps, then XW transform warps.
+// Roles: warps 0-3 softmax / epilogue, warp 4 MMA issue, then PW gather warps (the whole tile for an e4m3 cache;
+// only Q and the hybrid rope bytes next to transform warps), then XW transform warps.
 // Role in the reference: the MXFP4 split-KV stage-1 kernels (mixed-mla/submission.py:122-250,
 // mixed-mla/versions/hip_mxfp4_v5/submission.py:214-656) and their block decode
 // (mixed-mla/triton_mla_mxfp4.py:20-67).
@@ -40,7 +41,7 @@ constexpr int STAGE_BYTES = 4 * PANEL_BYTES + ROPE_PANEL_BYTES;    // 72 KB
 constexpr int SMEM_LIMIT = 232448;        // opt-in shared memory per CTA
 constexpr float RECENTER = 4.0f;          // log2 units
 constexpr float P_SCALE_LOG2 = 4.0f;      // probabilities are stored multiplied by 2^4
-constexpr int E_BIAS = 127 + 6;           // operand bytes of a block-scaled tile are in units of 2^(E_tile - E_BIAS)
+constexpr int E_BIAS = 127 + 6;           // operand bytes of a block-scaled unit are in units of 2^(E_unit - E_BIAS)
 
 // Optional timeline instrumentation (compiled in only with -DB200MLA_TRACE; development aid).
 #ifdef B200MLA_TRACE
