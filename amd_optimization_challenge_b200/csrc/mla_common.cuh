@@ -166,12 +166,18 @@ __device__ __forceinline__ uint2 q_cast_e4m3x8(const uint4& v, float scale) {
 // Scale of the e4m3 Q codes, the same value in every thread of the block.  All threads call it (it
 // synchronises the block when the scale has to be reduced from the partial maxima); `word` is one
 // 32-bit word of shared memory.
-__device__ inline float block_q_scale(const unsigned int* amax_parts, const float* q_scale, int q_cast, unsigned int* word) {
+// block_q_amax_begin issues this thread's loads of the partial maxima (call it early, the result is
+// only needed by block_q_scale); without a cast it returns 0 and touches nothing.
+__device__ __forceinline__ unsigned int block_q_amax_begin(const unsigned int* amax_parts, int q_cast) {
+    unsigned int m = 0;
+    if (q_cast)
+        for (int i = threadIdx.x; i < Q_AMAX_PARTS; i += blockDim.x) m = max(m, __ldg(amax_parts + i));
+    return m;
+}
+__device__ inline float block_q_scale(unsigned int m, const float* q_scale, int q_cast, unsigned int* word) {
     if (!q_cast) return q_scale ? __ldg(q_scale) : 1.0f;
     if (threadIdx.x == 0) *word = 0u;
     __syncthreads();
-    unsigned int m = 0;
-    for (int i = threadIdx.x; i < Q_AMAX_PARTS; i += blockDim.x) m = max(m, __ldg(amax_parts + i));
     m = __reduce_max_sync(0xffffffffu, m);
     if ((threadIdx.x & 31) == 0 && m) atomicMax(word, m);
     __syncthreads();

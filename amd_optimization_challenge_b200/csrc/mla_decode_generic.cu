@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(THREADS, 2) mla_decode_generic_kernel(const Ml
     if (t_begin >= t_end) return;
 
     // scalar scales: scores get q_scale * kv_scale(e4m3 cache) * sm_scale * log2e, outputs kv_scale
-    const float q_sc = p.q_format == Q_E4M3 ? block_q_scale(p.q_amax_parts, p.q_scale, p.q_cast, &s.q_amax) : 1.0f;
+    const float q_sc = p.q_format == Q_E4M3 ? block_q_scale(block_q_amax_begin(p.q_amax_parts, p.q_cast), p.q_scale, p.q_cast, &s.q_amax) : 1.0f;
     const float kv_sc = (KVFMT == KV_E4M3 || KVFMT == KV_HYBRID) ? __ldg(p.kv_scale) : 1.0f;
     const float score_scale = p.sm_scale * LOG2E * q_sc * (KVFMT == KV_E4M3 ? kv_sc : 1.0f);
     const float out_scale = KVFMT == KV_E4M3 ? kv_sc : 1.0f;

@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     const int w = blockIdx.x, G = p.num_ctas;
     const int row0 = blockIdx.y * N;
     if (tid == 0) TRACE(0, 63);
+    const unsigned int q_amax_local = block_q_amax_begin(p.q_amax_parts, p.q_cast);   // loads in flight during the prologue
 
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], PRODUCERS); mbar_init(&ms.kv_empty[i], 1); }
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
     const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
 
-    const float q_sc = block_q_scale(p.q_amax_parts, p.q_scale, p.q_cast, &ms.q_amax), kv_sc = __ldg(p.kv_scale);
+    const float q_sc = block_q_scale(q_amax_local, p.q_scale, p.q_cast, &ms.q_amax), kv_sc = __ldg(p.kv_scale);
     const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
     const float out_scale = kv_sc;
     volatile int* abort_flag = &ms.abort_flag;
@@ -159,33 +160,22 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             for (int g = 0; g < n_total; ++g) {
                 const int st = g % NS;
                 const bool first = wk.seek(p, prefix, t_begin + g);
-                if (first) {
-                    // Q rows of the new sequence -> swizzled K-major panels of Q buffer (pair & 1)
-                    const int qb = wk.pair & 1;
-                    mbar_wait(&ms.q_empty[qb], wk.pair / 2 - 1, abort_flag);
-                    const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
-                    if (p.q_cast) {
-                        // bf16 rows, quantised here: eight values in, eight e4m3 bytes (half a 16-byte column) out
-                        unsigned char* q_smem = smem + L::OFF_Q + qb * L::Q_BYTES;
-                        for (int i = pt; i < N * 72; i += PRODUCERS) {
-                            const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
-                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) +
-                                                       (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8;
-                            const uint2 o = q_cast_e4m3x8(__ldg(reinterpret_cast<const uint4*>(src)), q_sc);
-                            *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) = o;
-                        }
-                        fence_proxy_async();                      // the MMA reads Q through the async proxy
-                        mbar_arrive(&ms.q_full[qb]);
-                    } else {
-                        for (int i = pt; i < N * 36; i += PRODUCERS) {
-                            const int r = i / 36, c = i - r * 36;
-                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
-                                                 (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
-                            cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
-                        }
-                        cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
+                // Q rows of a new sequence.  A bf16 Q that is cast on load is fetched into registers now (when a thread's share
+                // is small) so that its latency runs beside the tile's copies; it is converted and stored after they are issued.
+                constexpr int QV = (N * 72 + PRODUCERS - 1) / PRODUCERS;     // 16-byte bf16 vectors per thread
+                constexpr bool Q_PRELOAD = QV <= 8;
+                uint4 qv[Q_PRELOAD ? QV : 1];
+                auto q_src = [&](int i) {
+                    const int r = i / 72, v8 = i - r * 72;
+                    const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                    return reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                                                          (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8);
+                };
+                if (first && p.q_cast && Q_PRELOAD) {
+#pragma unroll
+                    for (int k = 0; k < QV; ++k) {
+                        const int i = pt + k * PRODUCERS;
+                        qv[Q_PRELOAD ? k : 0] = i < N * 72 ? __ldg(q_src(i)) : make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
                 mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
@@ -222,6 +212,41 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 }
                 if (pt == 0) TRACE(1, g);
                 cp_async_mbar_arrive_noinc(&ms.kv_full[st]);   // asynchronous: the thread does not wait for its copies
+                if (first) {
+                    // Q rows of the new sequence -> swizzled K-major panels of Q buffer (pair & 1)
+                    const int qb = wk.pair & 1;
+                    mbar_wait(&ms.q_empty[qb], wk.pair / 2 - 1, abort_flag);
+                    const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
+                    if (p.q_cast) {
+                        // bf16 rows, quantised here: eight values in, eight e4m3 bytes (half a 16-byte column) out
+                        unsigned char* q_smem = smem + L::OFF_Q + qb * L::Q_BYTES;
+                        auto put = [&](int i, const uint4& raw) {
+                            const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
+                            *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) =
+                                q_cast_e4m3x8(raw, q_sc);
+                        };
+                        if (Q_PRELOAD) {
+#pragma unroll
+                            for (int k = 0; k < QV; ++k) {
+                                const int i = pt + k * PRODUCERS;
+                                if (i < N * 72) put(i, qv[Q_PRELOAD ? k : 0]);
+                            }
+                        } else {
+                            for (int i = pt; i < N * 72; i += PRODUCERS) put(i, __ldg(q_src(i)));
+                        }
+                        fence_proxy_async();                      // the MMA reads Q through the async proxy
+                        mbar_arrive(&ms.q_full[qb]);
+                    } else {
+                        for (int i = pt; i < N * 36; i += PRODUCERS) {
+                            const int r = i / 36, c = i - r * 36;
+                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
+                                                 (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
+                            cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
+                        }
+                        cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
+                    }
+                }
             }
             cp_async_wait_all();
         } else if (warp == 4) {

@@ -157,6 +157,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int w = blockIdx.x, G = p.num_ctas;
     const int row0 = blockIdx.y * N;
+    const unsigned int q_amax_local = block_q_amax_begin(p.q_amax_parts, QFMT == Q_E4M3 ? p.q_cast : 0);   // loads in flight during the prologue
 
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], C::KV_FULL_COUNT); mbar_init(&ms.kv_empty[i], 1); }
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
 
     const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
     const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
-    const float q_tensor_scale = QFMT == Q_E4M3 ? block_q_scale(p.q_amax_parts, p.q_scale, p.q_cast, &ms.q_amax) : 1.0f;
+    const float q_tensor_scale = QFMT == Q_E4M3 ? block_q_scale(q_amax_local, p.q_scale, p.q_cast, &ms.q_amax) : 1.0f;
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
