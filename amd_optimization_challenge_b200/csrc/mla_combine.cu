@@ -33,10 +33,11 @@ __global__ void __launch_bounds__(128) combine_spans_kernel(const MlaParams p) {
         if (p.out_lse && threadIdx.x == 0) p.out_lse[orow] = -INFINITY;
         return;
     }
-    const int w0 = cta_of_tile(t0, TT, G), w1 = cta_of_tile(t1 - 1, TT, G);
+    const int TU = total_units(TT, p.batch);              // schedule units: tiles plus the set-up units of every sequence
+    const int w0 = cta_of_tile(t0, b, TU, G), w1 = cta_of_tile(t1 - 1, b, TU, G);
     if (w0 == w1) return;                                 // finished by a single stage-1 CTA
     // streaming merge, four partials per step so that their loads are in flight together;
-    // CTAs whose span is empty (G > total tiles) wrote nothing and are skipped
+    // CTAs without any unit (G > total units) wrote nothing and are skipped
     float M = -INFINITY, den = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int wb = w0; wb <= w1; wb += 4) {
@@ -45,7 +46,9 @@ __global__ void __launch_bounds__(128) combine_spans_kernel(const MlaParams p) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int w = wb + u;
-            const bool ok = w <= w1 && span_begin(w, TT, G) < span_begin(w + 1, TT, G);
+            // w0 and w1 hold the sequence's first and last tile; a CTA in between holds tiles of this sequence
+            // only, unless it holds no unit at all
+            const bool ok = w <= w1 && (w == w0 || w == w1 || cta_has_units(w, TU, G));
             const long long slot = (long long)(w + b) * p.rows + r;
             l[u] = ok ? p.part_lse[slot] : -INFINITY;
             v[u] = ok ? *reinterpret_cast<const float4*>(p.part_o + slot * V_DIM + d) : make_float4(0.f, 0.f, 0.f, 0.f);

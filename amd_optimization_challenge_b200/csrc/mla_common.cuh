@@ -50,18 +50,44 @@ struct MlaParams {
 };
 
 // ---------------------------------------------------------------------------------------------
-// Schedule.  Sequence b owns tiles [P[b], P[b+1]) with ceil(len_b / tile_tokens) tiles; CTA w of
-// G owns the global tile range [w*TT/G, (w+1)*TT/G).  A (CTA, sequence) pair that does not cover
-// the whole sequence writes a partial into slot w + b, which is unique because both coordinates
-// are monotone along the chain of pairs.
+// Schedule.  Sequence b owns tiles [P[b], P[b+1]) with ceil(len_b / tile_tokens) tiles.  The work is
+// measured in units: one per tile plus SEQ_UNITS per sequence (its Q load, first-tile re-centering
+// and epilogues cost a CTA about as much as two tiles; measured on config 1, the CTAs that hold a
+// sequence boundary ran 10 % longer than the others under a plain tile split), so sequence b owns
+// units [P[b] + K*b, P[b+1] + K*(b+1)), K = SEQ_UNITS, the first K being set-up units.  CTA w of G
+// owns the units [w*TU/G, (w+1)*TU/G), TU = P[batch] + K*batch, i.e. the tiles those units stand
+// for.  A (CTA, sequence) pair that does not cover the whole sequence writes a partial into slot
+// w + b, which is unique because both coordinates are monotone along the chain of pairs.
 // ---------------------------------------------------------------------------------------------
+#ifndef B200MLA_SEQ_UNITS
+#define B200MLA_SEQ_UNITS 2
+#endif
+constexpr int SEQ_UNITS = B200MLA_SEQ_UNITS;
 
-__device__ __forceinline__ int span_begin(int w, int total_tiles, int G) {
-    return (int)(((long long)w * total_tiles) / G);
+__device__ __forceinline__ int total_units(int total_tiles, int batch) { return total_tiles + SEQ_UNITS * batch; }
+// Sequence that owns unit u: the first b with P[b+1] + K*(b+1) > u.
+__device__ __forceinline__ int seq_of_unit(const int* prefix, int batch, int u) {
+    int lo = 0, hi = batch - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid + 1] + SEQ_UNITS * (mid + 1) > u) hi = mid; else lo = mid + 1;
+    }
+    return lo;
 }
-// CTA whose span contains global tile t.
-__device__ __forceinline__ int cta_of_tile(int t, int total_tiles, int G) {
-    return (int)((((long long)(t + 1) * G + total_tiles - 1) / total_tiles) - 1);
+// First tile of CTA w's span (w = G gives the total number of tiles).
+__device__ __forceinline__ int span_begin(const int* prefix, int batch, int w, int G) {
+    if (w >= G) return prefix[batch];
+    const int u = (int)(((long long)w * total_units(prefix[batch], batch)) / G);
+    const int b = seq_of_unit(prefix, batch, u);
+    return max(prefix[b], u - SEQ_UNITS * (b + 1));
+}
+// CTA whose span contains tile t of sequence b (unit t + K*(b+1)).
+__device__ __forceinline__ int cta_of_tile(int t, int b, int units, int G) {
+    return (int)((((long long)(t + SEQ_UNITS * (b + 1) + 1) * G + units - 1) / units) - 1);
+}
+// Does CTA w own any unit at all (G may exceed the number of units)?
+__device__ __forceinline__ bool cta_has_units(int w, int units, int G) {
+    return ((long long)w * units) / G < ((long long)(w + 1) * units) / G;
 }
 
 // Fills prefix[0..batch] (shared memory) with the exclusive prefix of tiles per sequence.

@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(THREADS, 2) mla_decode_generic_kernel(const Ml
     if (w == 0 && blockIdx.y == 0)
         for (int i = tid; i <= p.batch; i += THREADS) p.tile_prefix[i] = prefix[i];
     if (TT == 0) return;
-    const int t_begin = span_begin(w, TT, G), t_end = span_begin(w + 1, TT, G);
+    const int t_begin = span_begin(prefix, p.batch, w, G), t_end = span_begin(prefix, p.batch, w + 1, G);
     if (t_begin >= t_end) return;
 
     // scalar scales: scores get q_scale * kv_scale(e4m3 cache) * sm_scale * log2e, outputs kv_scale

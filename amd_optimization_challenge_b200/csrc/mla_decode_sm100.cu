@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     if (w == 0 && blockIdx.y == 0)
         for (int i = tid; i <= p.batch; i += THREADS) p.tile_prefix[i] = prefix[i];
 
-    const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
+    const int t_begin = TT > 0 ? span_begin(prefix, p.batch, w, G) : 0, t_end = TT > 0 ? span_begin(prefix, p.batch, w + 1, G) : 0;
     const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
 
     const float q_sc = block_q_scale(q_amax_local, p.q_scale, p.q_cast, &ms.q_amax), kv_sc = __ldg(p.kv_scale);
@@ -232,7 +232,15 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                                 if (i < N * 72) put(i, qv[Q_PRELOAD ? k : 0]);
                             }
                         } else {
-                            for (int i = pt; i < N * 72; i += PRODUCERS) put(i, __ldg(q_src(i)));
+                            for (int i0 = pt; i0 < N * 72; i0 += 8 * PRODUCERS) {     // eight loads in flight, then their conversion
+                                uint4 raw[8];
+#pragma unroll
+                                for (int u = 0; u < 8; ++u)
+                                    if (i0 + u * PRODUCERS < N * 72) raw[u] = __ldg(q_src(i0 + u * PRODUCERS));
+#pragma unroll
+                                for (int u = 0; u < 8; ++u)
+                                    if (i0 + u * PRODUCERS < N * 72) put(i0 + u * PRODUCERS, raw[u]);
+                            }
                         }
                         fence_proxy_async();                      // the MMA reads Q through the async proxy
                         mbar_arrive(&ms.q_full[qb]);

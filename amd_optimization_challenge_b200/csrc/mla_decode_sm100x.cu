@@ -58,7 +58,9 @@ struct Cfg {
     static constexpr bool ROPE_SEP = KVFMT == KV_HYBRID;
     static constexpr int NQ = N * (QSPLIT ? 2 : 1);               // Q rows in shared memory = columns of one S accumulator
     static constexpr int SC = NQ * (ROPE_SEP ? 2 : 1);            // S columns per buffer
-    static constexpr int PW = XF ? 1 : (N == 16 ? 8 : 4);         // with transform warps the gather role only moves Q and rope bytes
+    // with transform warps the gather role only moves Q and rope bytes; N = 32 runs 3 warps per scheduler either
+    // way (registers are handed out per scheduler), so a hybrid cache's rope gather gets the two spare warps
+    static constexpr int PW = XF ? ((N == 32 && ROPE_SEP) ? 3 : 1) : (N == 16 ? 8 : 4);
     static constexpr int XW = XF ? (N == 16 ? 8 : 4) : 0;
     static constexpr int PRODUCERS = 32 * PW, XT = 32 * XW;
     static constexpr int THREADS = 160 + PRODUCERS + XT;
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
     if (w == 0 && blockIdx.y == 0)
         for (int i = tid; i <= p.batch; i += THREADS) p.tile_prefix[i] = prefix[i];
 
-    const int t_begin = TT > 0 ? span_begin(w, TT, G) : 0, t_end = TT > 0 ? span_begin(w + 1, TT, G) : 0;
+    const int t_begin = TT > 0 ? span_begin(prefix, p.batch, w, G) : 0, t_end = TT > 0 ? span_begin(prefix, p.batch, w + 1, G) : 0;
     const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
     const float q_tensor_scale = QFMT == Q_E4M3 ? block_q_scale(q_amax_local, p.q_scale, p.q_cast, &ms.q_amax) : 1.0f;
     volatile int* abort_flag = &ms.abort_flag;
@@ -265,15 +267,29 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     if (!C::QSPLIT && p.q_cast) {
                         // bf16 rows, quantised here: eight values in, eight e4m3 bytes (half a 16-byte column) out
                         unsigned char* q_smem = smem + C::OFF_Q;
-                        for (int i = pt; i < N * 72; i += PRODUCERS) {
-                            const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
-                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) +
-                                                       (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8;
-                            const uint2 o = q_cast_e4m3x8(__ldg(reinterpret_cast<const uint4*>(src)), q_tensor_scale);
-                            const int off = c < 32 ? (c >> 3) * C::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)
-                                                   : 4 * C::Q_PANEL_BYTES + r * 64 + (((c - 32) ^ ((r >> 1) & 3)) << 4);
-                            *reinterpret_cast<uint2*>(q_smem + off + (v8 & 1) * 8) = o;
+                        // eight loads in flight per thread, then their conversion (a few gather threads serve many rows)
+                        for (int i0 = pt; i0 < N * 72; i0 += 8 * PRODUCERS) {
+                            uint4 raw[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int i = i0 + u * PRODUCERS;
+                                if (i < N * 72) {
+                                    const int r = i / 72, v8 = i - r * 72;
+                                    const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                                    raw[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                                                   (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8));
+                                }
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int i = i0 + u * PRODUCERS;
+                                if (i < N * 72) {
+                                    const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
+                                    const int off = c < 32 ? (c >> 3) * C::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)
+                                                           : 4 * C::Q_PANEL_BYTES + r * 64 + (((c - 32) ^ ((r >> 1) & 3)) << 4);
+                                    *reinterpret_cast<uint2*>(q_smem + off + (v8 & 1) * 8) = q_cast_e4m3x8(raw[u], q_tensor_scale);
+                                }
+                            }
                         }
                         fence_proxy_async();                      // the MMA reads Q through the async proxy
                         mbar_arrive(&ms.q_full);

@@ -235,8 +235,13 @@ def custom_kernel(data):
     if q.dtype == torch.bfloat16 and q_format == "fp8":
         # the reference quantises Q per tensor before its FP8 kernels (reference.py:65-80, 308-310); here only the
         # amax is a launch of its own, the cast happens where the decode kernel loads Q
+        # (for 16 query rows per sequence; with more rows per CTA the kernels' few gather threads would spend longer
+        # on the cast than the separate cast launch costs)
         q = q.contiguous()
-        q_scale, q_cast = q_amax_parts(q), True
+        if (q.shape[1] * q_len) % 32 != 0:
+            q_scale, q_cast = q_amax_parts(q), True
+        else:
+            q, q_scale = quantize_q_fp8(q)
     elif q.dtype != torch.bfloat16:
         q_scale = config["q_scale"]
     if "total_kv" in config:
