@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     const int row0 = blockIdx.y * N;
     if (tid == 0) TRACE(0, 63);
     const unsigned int q_amax_local = block_q_amax_begin(p.q_amax_parts, p.q_cast);   // loads in flight during the prologue
+    const float kv_sc = __ldg(p.kv_scale);       // issued here, first used by the softmax role: no role waits for it at its start
 
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], PRODUCERS); mbar_init(&ms.kv_empty[i], 1); }
@@ -130,9 +131,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     const int t_begin = TT > 0 ? span_begin(prefix, p.batch, w, G) : 0, t_end = TT > 0 ? span_begin(prefix, p.batch, w + 1, G) : 0;
     const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
 
-    const float q_sc = block_q_scale(q_amax_local, p.q_scale, p.q_cast, &ms.q_amax), kv_sc = __ldg(p.kv_scale);
-    const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
-    const float out_scale = kv_sc;
+    const float q_sc = block_q_scale(q_amax_local, p.q_scale, p.q_cast, &ms.q_amax);
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
@@ -344,6 +343,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             }
         } else {
             // =========================== softmax / correction / epilogue (128 threads) ===========
+            const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
+            const float out_scale = kv_sc;
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
             Walker wk; wk.init(prefix, p.batch, t_begin);
             // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key

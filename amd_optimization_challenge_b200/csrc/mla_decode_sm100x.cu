@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
     const int w = blockIdx.x, G = p.num_ctas;
     const int row0 = blockIdx.y * N;
     const unsigned int q_amax_local = block_q_amax_begin(p.q_amax_parts, QFMT == Q_E4M3 ? p.q_cast : 0);   // loads in flight during the prologue
+    const float kv_tensor_scale = KVFMT != KV_MXFP4 ? __ldg(p.kv_scale) : 1.0f;   // issued here, first used by the softmax role
 
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], C::KV_FULL_COUNT); mbar_init(&ms.kv_empty[i], 1); }
@@ -537,7 +538,6 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             // =========================== softmax / correction / epilogue (128 threads) ===========
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
             Walker wk; wk.init(prefix, p.batch, t_begin);
-            const float kv_tensor_scale = KVFMT != KV_MXFP4 ? __ldg(p.kv_scale) : 1.0f;
             float qk_base = 0.0f;          // sm_scale * log2(e) * (scale of this sequence's Q bytes)
             int e_run = 0;                 // exponent frame of O (block-scaled caches)
             // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key
