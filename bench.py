@@ -415,8 +415,13 @@ def main():
                "sample": f"median of {args.cpu_reps} full {args.workload} calls ({t_cpu * 1e3:.1f} ms each)",
                "us_per_call": t_cpu * 1e6}
 
-    # stage 1 + combine, plus the amax of an FP8-cast Q or the e4m3 split of a bf16 Q (tcgen05 kernels only)
-    launches_per_step = 2 + (1 if (w["q_format"] == "fp8" or args.kernel != "generic") else 0)
+    # stage 1 + combine; an FP8-cast Q adds its amax launch (16 query rows per sequence: the cast happens inside
+    # stage 1) or amax + cast (more rows); a bf16 Q adds its e4m3 split (tcgen05 kernels only)
+    rows = w["heads"] * w["q_len"]
+    if w["q_format"] == "fp8":
+        launches_per_step = 2 + (1 if rows % 32 != 0 else 2)
+    else:
+        launches_per_step = 2 + (1 if args.kernel != "generic" else 0)
     if mode == "split_kv":
         launches_per_step += 1                                        # merge of the gathered partials
     per_gpu = {"replica": "each rank decodes its own batch, no collective",
