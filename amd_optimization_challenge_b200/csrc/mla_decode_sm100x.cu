@@ -60,8 +60,8 @@ struct Cfg {
     static constexpr int SC = NQ * (ROPE_SEP ? 2 : 1);            // S columns per buffer
     // with transform warps the gather role only moves Q and rope bytes; N = 32 runs 3 warps per scheduler either
     // way (registers are handed out per scheduler), so a hybrid cache's rope gather gets the two spare warps
-    static constexpr int PW = XF ? ((N == 32 && ROPE_SEP) ? 3 : 1) : (N == 16 ? 8 : 4);
-    static constexpr int XW = XF ? (N == 16 ? 8 : 4) : 0;
+    static constexpr int PW = XF ? 1 : (N == 16 ? 8 : 4);
+    static constexpr int XW = XF ? ((N == 16 || (ROPE_SEP && !QSPLIT)) ? 8 : 4) : 0;
     static constexpr int PRODUCERS = 32 * PW, XT = 32 * XW;
     static constexpr int THREADS = 160 + PRODUCERS + XT;
     static constexpr int NB = KVFMT == KV_MXFP4 ? 18 : 16;        // 32-code blocks per cache row
@@ -597,36 +597,37 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 }
                 const float a_lat = C::XF ? qk_base * pow2i(e_unit - E_BIAS) : qk_base * kv_tensor_scale;
                 const float a_rope = qk_base * kv_tensor_scale;
-                // s[c] = score of (this thread's token, query row c) in log2 units
-                float s[N];
+                // score of (this thread's token, query row c) in log2 units, read from the S accumulators.  The scores are not
+                // kept in registers beyond x: the rare re-centering path reads them again (the S buffer is handed back after it).
                 const uint32_t s_addr = tmem + lane_base + sb * C::SC;
+                auto load_scores = [&](float (&dst)[N]) {
 #pragma unroll
-                for (int c0 = 0; c0 < N; c0 += 16) {
-                    float v[16], vl[16], r[16], rl[16];
-                    tmem_ld16(s_addr + c0, v);
-                    if (C::QSPLIT) tmem_ld16(s_addr + N + c0, vl);
-                    if (C::ROPE_SEP) {
-                        tmem_ld16(s_addr + NQ + c0, r);
-                        if (C::QSPLIT) tmem_ld16(s_addr + NQ + N + c0, rl);
-                    }
-                    tmem_wait_ld();
+                    for (int c0 = 0; c0 < N; c0 += 16) {
+                        float v[16], vl[16], r[16], rl[16];
+                        tmem_ld16(s_addr + c0, v);
+                        if (C::QSPLIT) tmem_ld16(s_addr + N + c0, vl);
+                        if (C::ROPE_SEP) {
+                            tmem_ld16(s_addr + NQ + c0, r);
+                            if (C::QSPLIT) tmem_ld16(s_addr + NQ + N + c0, rl);
+                        }
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        float lat = v[c], rope = 0.0f;
-                        if (C::QSPLIT) lat = fmaf(vl[c], 0.0625f, lat);
-                        if (C::ROPE_SEP) { rope = r[c]; if (C::QSPLIT) rope = fmaf(rl[c], 0.0625f, rope); }
-                        s[c0 + c] = C::ROPE_SEP ? fmaf(rope, a_rope, lat * a_lat) : lat * a_lat;
+                        for (int c = 0; c < 16; ++c) {
+                            float lat = v[c], rope = 0.0f;
+                            if (C::QSPLIT) lat = fmaf(vl[c], 0.0625f, lat);
+                            if (C::ROPE_SEP) { rope = r[c]; if (C::QSPLIT) rope = fmaf(rl[c], 0.0625f, rope); }
+                            dst[c0 + c] = C::ROPE_SEP ? fmaf(rope, a_rope, lat * a_lat) : lat * a_lat;
+                        }
                     }
-                }
-                tc_fence_before();
-                mbar_arrive(&ms.s_empty[sb]);
+                };
 
                 // x = log2-domain exponent of the stored probability: score - m_ref + P_SCALE_LOG2
                 const int pos = pos_first + tid;
                 const bool masked_tile = pos_first + TILE > lim_min;                 // uniform
                 float x[N];
+                load_scores(x);
 #pragma unroll
-                for (int c = 0; c < N; ++c) x[c] = s[c] + nm[c];
+                for (int c = 0; c < N; ++c) x[c] += nm[c];
                 if (masked_tile) {
 #pragma unroll
                     for (int c = 0; c < N; ++c) if (pos >= lim[c / 16]) x[c] = -INFINITY;
@@ -647,9 +648,10 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
 #pragma unroll
                     for (int c = 0; c < N; ++c) f[c] = 1.0f;
                     if (recenter) {
-                        float mx[N];
+                        float sv[N], mx[N];
+                        load_scores(sv);
 #pragma unroll
-                        for (int c = 0; c < N; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : s[c];
+                        for (int c = 0; c < N; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : sv[c];
                         reduce_cols(mx, true);
 #pragma unroll
                         for (int c = 0; c < N; ++c) {
@@ -659,7 +661,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                             any |= f[c] != 1.0f;
                             nm[c] = P_SCALE_LOG2 - m_new;
                             l_acc[c] *= f[c];
-                            x[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : s[c] + nm[c];
+                            x[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : sv[c] + nm[c];
                         }
                     }
                     if (!first && any) {
@@ -683,6 +685,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                         tc_fence_before();
                     }
                 }
+                tc_fence_before();
+                mbar_arrive(&ms.s_empty[sb]);                     // the scores have been read for the last time
                 // stored probability = p * 2^4 * 2^(e_unit - e_run): this token's V bytes are in the frame e_unit, O in e_run
                 const float p_frame = C::XF ? pow2i(e_unit - e_run) : 1.0f;
                 // P(g) may overwrite its buffer once PV(g-2) has completed
