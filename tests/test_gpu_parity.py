@@ -422,3 +422,26 @@ def test_q_cast_on_load_equals_two_step_quantisation(pkg, impl, kv_format):
         fused = pkg.mla_decode(q, pkg.q_amax_parts(q), kv_format, kvd[kv_format], ip, q_cast=True, **common)
         torch.cuda.synchronize()
         assert torch.equal(two_step, fused)
+
+
+def test_random_shapes_tcgen05_matches_warp_level_kernel(pkg):
+    """Forty random problems (format pair, heads, q_len, ragged lengths incl. empty and tile-edge ones, page
+    shuffling, CTA count): the tcgen05 kernels against the warp-level kernel, which shares only the schedule."""
+    import random
+    rnd = random.Random(2024)
+    for case in range(40):
+        kvf, qf = rnd.choice([("fp8", "fp8"), ("fp8", "bf16"), ("mxfp4", "bf16"), ("mxfp4", "fp8"),
+                              ("hybrid", "fp8"), ("hybrid", "bf16")])
+        heads = rnd.choice([16, 16, 32, 64, 128])
+        q_len = rnd.choice([1, 1, 2, 4]) if heads <= 32 else 1
+        batch = rnd.randint(1, 9)
+        lens = [rnd.choice([0, 1, 5, 111, 112, 113, 127, 128, 129, 300, 1000, rnd.randint(1, 3000)]) for _ in range(batch)]
+        if sum(lens) == 0:
+            lens[0] = 7
+        data = pkg.generate_input(batch, q_len, max(lens), seed=case, kv_lens=lens, shuffle_pages=rnd.random() < 0.7,
+                                  num_heads=heads, formats=(kvf,))
+        cfg = dict(data[4]); cfg["max_ctas"] = rnd.choice([0, 0, 1, 2, 3, 5, 17])
+        d = (data[0], data[1], data[2], data[3], cfg)
+        a = _run(pkg, d, kvf, qf, "generic")
+        b = _run(pkg, d, kvf, qf, "tcgen05")
+        assert_close(b, a, rtol=2e-2, atol=2e-3)
