@@ -444,4 +444,5 @@ def test_random_shapes_tcgen05_matches_warp_level_kernel(pkg):
         d = (data[0], data[1], data[2], data[3], cfg)
         a = _run(pkg, d, kvf, qf, "generic")
         b = _run(pkg, d, kvf, qf, "tcgen05")
-        assert_close(b, a, rtol=2e-2, atol=2e-3)
+        # two independent approximations: the tolerance of record plus 2 % of the output scale
+        assert_close(b, a, tight=2e-2)
