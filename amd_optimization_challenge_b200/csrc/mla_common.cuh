@@ -136,8 +136,6 @@ __device__ __forceinline__ long long slot_of(const MlaParams& p, int b, int seq_
     return (long long)p.kv_indices[page_base + pg] * p.page_size + (pos - pg * p.page_size);
 }
 
-constexpr int WALK_TILE = 128;   // tokens per tile of the tcgen05 kernels (the walker below is theirs)
-
 // Position of one role inside the CTA's span of global tiles [t_begin, t_end): which sequence the
 // current tile belongs to, and that sequence's geometry.  Every role walks the span with its own copy.
 struct Walker {
