@@ -52,6 +52,9 @@ KV_ROW_BYTES = {"fp8": 576, "mxfp4": 306, "hybrid": 336}
 # how a workload uses N > 1 GPUs: independent replicas (weak scaling), a token-balanced split of the
 # batch (strong, no collective), or each sequence's keys split over the GPUs (strong, one all-gather)
 MODES = {"c1": "replica", "c2": "replica", "c3": "batch_shard", "c4": "split_kv"}
+# DRAM bytes read + written by one stage-1 launch, from one ncu capture of that workload on one GPU
+# (profiles/ holds the capture's summary and command); None where no capture was taken.
+NCU_TRAFFIC_BYTES = {"c1": 78.8e6, "c2": 191.9e6}
 L2_BYTES = 126 << 20
 
 
@@ -367,7 +370,8 @@ def main():
     peak, peak_kind = measured_peak_gbs()
     achieved = abytes / (k_us * 1e-6) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "kernel": "mla_decode stage 1", "kernel_us": k_us,
+                "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if mode == "replica" else None, "traffic_unit": "bytes per launch (ncu dram read + write, separate capture)",
+                "kernel": "mla_decode stage 1", "kernel_us": k_us,
                 "algorithmic_bytes": abytes, "peak_source": f"of {peak_kind}"}
 
     # ---- end to end: host buffers in, host buffer out, every step
