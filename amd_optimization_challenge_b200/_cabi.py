@@ -38,7 +38,8 @@ class DecodeArgs(ctypes.Structure):
 
 EXPORTS = ("b200_mla_version", "b200_mla_last_error", "b200_mla_workspace_bytes", "b200_mla_decode",
            "b200_mla_combine", "b200_mla_quantize_fp8", "b200_mla_q_amax", "b200_mla_set_stage1_events",
-           "b200_mla_decode_static")
+           "b200_mla_decode_static", "b200_mla_read_status", "b200_mla_reset_status")
+STATUS_TIMEOUT, STATUS_BAD_PAGE = 1, 2
 
 
 def _load() -> ctypes.CDLL:
@@ -61,6 +62,10 @@ def _load() -> ctypes.CDLL:
     lib.b200_mla_q_amax.argtypes = [_vp, _i64, _vp, _vp]
     lib.b200_mla_decode_static.restype = _i32
     lib.b200_mla_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), _vp]
+    lib.b200_mla_read_status.restype = _i32
+    lib.b200_mla_read_status.argtypes = [_vp, _vp, _vp]
+    lib.b200_mla_reset_status.restype = _i32
+    lib.b200_mla_reset_status.argtypes = [_vp, _vp]
     lib.b200_mla_set_stage1_events.restype = _i32
     lib.b200_mla_set_stage1_events.argtypes = [_vp, _vp]
     return lib

@@ -118,6 +118,7 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
         return fail(B200_MLA_ERR_INVALID_ARG, "kv_page_indptr is required when page_size > 1");
     if (!a->out && !a->out_o_f32) return fail(B200_MLA_ERR_INVALID_ARG, "one of out / out_o_f32 is required");
     if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(B200_MLA_ERR_INVALID_ARG, "workspace must be non-NULL and 256-byte aligned");
+    if (a->num_slots <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "num_slots (rows of the cache planes) must be positive: page ids are checked against it");
 
     MlaParams p;
     memset(&p, 0, sizeof(p));
@@ -157,8 +158,7 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     }
     else { p.tile_tokens = 64; p.rows_per_cta = 16; ctas_per_sm = 2; }
     const int groups = p.rows / p.rows_per_cta;
-    long long hint = a->total_kv_hint > 0 ? a->total_kv_hint : a->num_slots;
-    if (hint <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "total_kv_hint or num_slots must be positive");
+    const long long hint = a->total_kv_hint > 0 ? a->total_kv_hint : a->num_slots;
     const long long tiles_bound = (hint + p.tile_tokens - 1) / p.tile_tokens + a->batch;
     long long G = (long long)ctas_per_sm * sms / groups;
     if (G < 1) G = 1;
@@ -170,6 +170,7 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     if (a->workspace_bytes < L.total)
         return fail(B200_MLA_ERR_WORKSPACE, "workspace of %lld bytes is smaller than the %lld required", (long long)a->workspace_bytes, L.total);
     char* ws = (char*)a->workspace;
+    p.status = (int*)(ws + L.status_off);
     p.tile_prefix = (int*)(ws + L.prefix_off);
     p.part_lse = (float*)(ws + L.lse_off);
     p.part_o = (float*)(ws + L.o_off);
@@ -193,19 +194,9 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
 // Scratch of the allocation-free entry point: lives in the library image, one copy per GPU.
 static __device__ __align__(256) unsigned char g_static_workspace[B200_MLA_STATIC_WORKSPACE_BYTES];
 
-extern "C" {
-
-int32_t b200_mla_decode_static(const b200_mla_decode_args* args, void* stream) {
-    if (!args) return fail(B200_MLA_ERR_INVALID_ARG, "args is NULL");
-    if (args->batch <= 0 || args->heads <= 0 || args->q_len <= 0)
-        return fail(B200_MLA_ERR_INVALID_ARG, "batch/heads/q_len must be positive");
-    const long long need = b200_mla_workspace_bytes(args->batch, args->heads, args->q_len);
-    if (need > (long long)B200_MLA_STATIC_WORKSPACE_BYTES)
-        return fail(B200_MLA_ERR_TOO_LARGE,
-                    "this problem needs %lld bytes of scratch, the built-in scratch of b200_mla_decode_static holds %u; "
-                    "use b200_mla_decode with a caller-provided workspace", need, (unsigned)B200_MLA_STATIC_WORKSPACE_BYTES);
-    // In host code the array's name is only a handle; its device address is looked up once per
-    // device, with that device current.
+// Device address of the built-in scratch on the current device.  In host code the array's name is
+// only a handle; its device address is looked up once per device, with that device current.
+static int static_workspace_ptr(void** out) {
     constexpr int kMaxDevices = 64;
     static void* dev_ptr[kMaxDevices] = {};
     int dev = 0;
@@ -219,10 +210,50 @@ int32_t b200_mla_decode_static(const b200_mla_decode_args* args, void* stream) {
             return fail(B200_MLA_ERR_CUDA, "cudaGetSymbolAddress(static workspace) failed: %s", cudaGetErrorString(e));
         __atomic_store_n(&dev_ptr[dev], ptr, __ATOMIC_RELEASE);
     }
+    *out = ptr;
+    return B200_MLA_OK;
+}
+
+extern "C" {
+
+int32_t b200_mla_decode_static(const b200_mla_decode_args* args, void* stream) {
+    if (!args) return fail(B200_MLA_ERR_INVALID_ARG, "args is NULL");
+    if (args->batch <= 0 || args->heads <= 0 || args->q_len <= 0)
+        return fail(B200_MLA_ERR_INVALID_ARG, "batch/heads/q_len must be positive");
+    const long long need = b200_mla_workspace_bytes(args->batch, args->heads, args->q_len);
+    if (need > (long long)B200_MLA_STATIC_WORKSPACE_BYTES)
+        return fail(B200_MLA_ERR_TOO_LARGE,
+                    "this problem needs %lld bytes of scratch, the built-in scratch of b200_mla_decode_static holds %u; "
+                    "use b200_mla_decode with a caller-provided workspace", need, (unsigned)B200_MLA_STATIC_WORKSPACE_BYTES);
+    void* ptr = nullptr;
+    const int rc = static_workspace_ptr(&ptr);
+    if (rc != B200_MLA_OK) return rc;
     b200_mla_decode_args a = *args;
     a.workspace = ptr;
     a.workspace_bytes = B200_MLA_STATIC_WORKSPACE_BYTES;
     return b200_mla_decode(&a, stream);
+}
+
+int32_t b200_mla_read_status(const void* workspace, int32_t* out, void* stream) {
+    if (!out) return fail(B200_MLA_ERR_INVALID_ARG, "out is NULL");
+    void* ws = const_cast<void*>(workspace);
+    if (!ws) {
+        const int rc = static_workspace_ptr(&ws);
+        if (rc != B200_MLA_OK) return rc;
+    }
+    cudaError_t e = cudaMemcpyAsync(out, ws, sizeof(int32_t), cudaMemcpyDefault, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "status copy failed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_reset_status(void* workspace, void* stream) {
+    if (!workspace) {
+        const int rc = static_workspace_ptr(&workspace);
+        if (rc != B200_MLA_OK) return rc;
+    }
+    cudaError_t e = cudaMemsetAsync(workspace, 0, 256, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "status reset failed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
 }
 
 int32_t b200_mla_set_stage1_events(void* start_event, void* stop_event) {

@@ -22,6 +22,8 @@ constexpr float LN2 = 0.6931471805599453f;
 enum { Q_BF16 = 0, Q_E4M3 = 1 };
 constexpr int Q_AMAX_PARTS = 256;      // partial maxima handed over by the amax kernel when Q is cast on load
 enum { KV_E4M3 = 0, KV_MXFP4 = 1, KV_HYBRID = 2 };
+// Bits of the sticky status word at the head of the workspace (B200_MLA_STATUS_* in b200_mla.h).
+enum { ST_OK = 0, ST_TIMEOUT = 1, ST_BAD_PAGE = 2 };
 
 struct MlaParams {
     int batch, heads, q_len, rows;      // rows = q_len * heads (query rows per sequence)
@@ -45,6 +47,7 @@ struct MlaParams {
     int* tile_prefix;                   // [batch + 1] exclusive prefix of tiles per sequence
     uint8_t* q_split;                   // bf16 Q as two e4m3 planes [2][batch * rows][576] (tcgen05 kernels)
     float* q_split_scale;               // [batch][rows / rows_per_cta] factor that undoes the planes' scaling
+    int* status;                        // sticky status word (bits ST_*), first word of the workspace
     int q_cast;                         // q is bf16 and is quantised to e4m3 (per-tensor, reference rule) as it is loaded;
     const unsigned int* q_amax_parts;   //   its scale comes from these Q_AMAX_PARTS partial maxima (bf16 bit patterns)
 };
@@ -128,12 +131,22 @@ __device__ __forceinline__ int seq_of_tile(const int* prefix, int batch, int t) 
     return lo;
 }
 
-// Cache slot of the token at position `pos` of sequence b.
+// Cache slot of the token at position `pos` of sequence b, or -1 when the page table points outside the
+// cache planes (slot < 0 or >= num_slots).  Such a row is never read: the callers treat it like a row past
+// the end of the sequence (zero fill), and the ST_BAD_PAGE bit of the status word tells the host about it.
 __device__ __forceinline__ long long slot_of(const MlaParams& p, int b, int seq_base, int page_base, int pos) {
-    if (p.kv_indices == nullptr) return (long long)seq_base + pos;
-    if (p.page_size == 1) return (long long)p.kv_indices[page_base + pos];
-    int pg = pos / p.page_size;
-    return (long long)p.kv_indices[page_base + pg] * p.page_size + (pos - pg * p.page_size);
+    long long s;
+    if (p.kv_indices == nullptr) s = (long long)seq_base + pos;
+    else if (p.page_size == 1) s = (long long)p.kv_indices[page_base + pos];
+    else {
+        const int pg = pos / p.page_size;
+        s = (long long)p.kv_indices[page_base + pg] * p.page_size + (pos - pg * p.page_size);
+    }
+    if (s < 0 || s >= p.num_slots) {
+        atomicOr(p.status, (int)ST_BAD_PAGE);
+        return -1;
+    }
+    return s;
 }
 
 // Position of one role inside the CTA's span of global tiles [t_begin, t_end): which sequence the
@@ -155,7 +168,7 @@ struct Walker {
         seq_t0 = prefix[b];
         seq_t1 = prefix[b + 1];
         seq_base = p.kv_indptr[b];
-        seq_len = p.kv_indptr[b + 1] - seq_base;
+        seq_len = max(p.kv_indptr[b + 1] - seq_base, 0);
         page_base = p.kv_page_indptr ? p.kv_page_indptr[b] : seq_base;
         pos_off = p.kv_pos_offset ? p.kv_pos_offset[b] : 0;
         tot_len = p.kv_total_len ? p.kv_total_len[b] : seq_len;

@@ -62,7 +62,8 @@ __device__ __forceinline__ void load_tile(const MlaParams& p, int b, int seq_bas
         r.v[i] = make_uint4(0, 0, 0, 0);
         r.sc[i] = 127;
         if (tok < TILE && pos < pos_end) {
-            long long slot = slot_of(p, b, seq_base, page_base, pos);
+            const long long slot = slot_of(p, b, seq_base, page_base, pos);
+            if (slot < 0) continue;                    // page id outside the cache: the row reads as zeros
             if (KVFMT == KV_E4M3) {
                 r.v[i] = __ldg(reinterpret_cast<const uint4*>(p.kv_codes + slot * p.kv_codes_stride) + c);
             } else if (KVFMT == KV_MXFP4) {
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(THREADS, 2) mla_decode_generic_kernel(const Ml
         const int seq_t0 = prefix[b], seq_t1 = prefix[b + 1];
         const int my_t1 = min(t_end, seq_t1);
         const int seq_base = p.kv_indptr[b];
-        const int seq_len = p.kv_indptr[b + 1] - seq_base;
+        const int seq_len = max(p.kv_indptr[b + 1] - seq_base, 0);
         const int page_base = p.kv_page_indptr ? p.kv_page_indptr[b] : seq_base;
         const int pos_off = p.kv_pos_offset ? p.kv_pos_offset[b] : 0;
         const int tot_len = p.kv_total_len ? p.kv_total_len[b] : seq_len;

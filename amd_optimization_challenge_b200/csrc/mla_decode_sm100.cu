@@ -16,8 +16,9 @@
 // waits until the epilogue has read O out of TMEM).
 //
 // Roles:  warps 0-3  softmax / correction / epilogue (one TMEM lane = one token / one output dim per thread)
-//         warp  4    tcgen05.mma issue (one lane, event driven), TMEM allocation
-//         warps 5..  paged gather: 16-byte cp.async of cache rows (and of Q) through the page table
+//         warp  4    tcgen05.mma issue of the QK stream (one lane), TMEM allocation
+//         warp  5    tcgen05.mma issue of the PV stream (one lane)
+//         warps 6..  paged gather: 16-byte cp.async of cache rows (and of Q) through the page table
 //                    straight into the 128B-swizzled UMMA layout, completion signalled on an mbarrier.
 // Movers measured on B200 for shuffled 576-byte rows, device-wide, one CTA per SM:
 //         16-byte cp.async (LSU)                       3.5 - 4.4 TB/s, lands directly in operand layout
@@ -41,15 +42,6 @@ constexpr int NS_MAX = 3;
 constexpr int SMEM_LIMIT = 232448;        // opt-in shared memory per CTA
 constexpr float RECENTER = 4.0f;          // log2 units
 constexpr float P_SCALE_LOG2 = 4.0f;      // probabilities are stored multiplied by 2^4
-// Optional timeline instrumentation (compiled in only with -DB200MLA_TRACE; development aid).
-#ifdef B200MLA_TRACE
-__device__ long long* g_trace = nullptr;
-#define TRACE(id, tile) do { if (g_trace && blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_trace[(tile) * 16 + (id)] = clock64(); \
-    if (g_trace && (tile) == 63 && ((id) == 0 || (id) == 5)) { unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt)); g_trace[1024 + blockIdx.x * 2 + ((id) == 5)] = (long long)gt; } } while (0)
-#else
-#define TRACE(id, tile) do { } while (0)
-#endif
-
 
 // ----------------------------------------------------------------------------------------------
 // N = 16: three stages of 112-token tiles (63 KB each).  Every MMA still spans 128 rows: rows 112..127 of a QK
@@ -66,9 +58,10 @@ struct Layout {
     static constexpr int ROPE_PANEL_BYTES = TILE * 64;           // dims 512..575: 64-byte rows, 64B swizzle
     static constexpr int STAGE_BYTES = 4 * PANEL_BYTES + ROPE_PANEL_BYTES;
     static constexpr int NPANEL = 5;                             // Q keeps five 128-byte-wide panels
-    static constexpr int PRODUCER_WARPS = (N == 16) ? 11 : 2;    // 512 threads at 128 registers; N = 32 needs the registers
+    static constexpr int PRODUCER_WARPS = (N == 16) ? 10 : 2;    // 512 threads at 128 registers; N = 32 needs the registers
     static constexpr int PRODUCERS = 32 * PRODUCER_WARPS;
-    static constexpr int THREADS = 160 + PRODUCERS;
+    static constexpr int FIRST_PRODUCER = 192;                     // warps 0-3 softmax, 4 QK issue, 5 PV issue
+    static constexpr int THREADS = FIRST_PRODUCER + PRODUCERS;
     static constexpr int Q_PANEL_BYTES = N * 128;
     static constexpr int Q_BYTES = NPANEL * Q_PANEL_BYTES;        // one Q buffer (two of them: next sequence's Q loads early)
     static constexpr int P_CHUNKS = 2 * N / 16;                  // 16-column chunks of [hi | lo]
@@ -104,7 +97,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int w = blockIdx.x, G = p.num_ctas;
     const int row0 = blockIdx.y * N;
-    if (tid == 0) TRACE(0, 63);
     const unsigned int q_amax_local = block_q_amax_begin(p.q_amax_parts, p.q_cast);   // loads in flight during the prologue
     const float kv_sc = __ldg(p.kv_scale);       // issued here, first used by the softmax role: no role waits for it at its start
 
@@ -123,7 +115,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     build_tile_prefix(p.kv_indptr, p.batch, TILE, prefix);       // ends with __syncthreads()
     tc_fence_after();
     const uint32_t tmem = ms.tmem_base;
-    if (tid == 0) TRACE(1, 63);
     const int TT = prefix[p.batch];
     if (w == 0 && blockIdx.y == 0)
         for (int i = tid; i <= p.batch; i += THREADS) p.tile_prefix[i] = prefix[i];
@@ -135,11 +126,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
-        if (warp >= 5) {
+        if (warp >= 6) {
             // =========================== gather ===========================
             // One stage = 128 tokens x 36 sixteen-byte columns.  Consecutive threads take consecutive
             // columns, so a warp instruction reads 512 contiguous bytes of (at most two) rows.
-            const int pt = tid - 160;
+            const int pt = tid - L::FIRST_PRODUCER;
             Walker wk; wk.init(prefix, p.batch, t_begin);
             Walker wn = wk;                                       // one tile ahead, for the page-table prefetch
             // thread pt looks up the page table for tokens pt, pt + PRODUCERS, ... of a tile (-1 past the end)
@@ -182,7 +173,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 for (int k = 0; k < SLOTS_PER_THREAD; ++k)
                     if (pt + k * PRODUCERS < TILE) ms.slot[st][pt + k * PRODUCERS] = my_slot[k];
                 named_bar_sync(2, PRODUCERS);                   // slots of this tile visible to every gather thread
-                if (pt == 0) TRACE(0, g);
                 slots_for(g + 1);
                 const uint32_t stage_addr = smem_base + st * STAGE_BYTES;
                 // Slots first, then the copies, if possible for the whole tile at once: a shared-memory load that sits
@@ -209,7 +199,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         }
                     }
                 }
-                if (pt == 0) TRACE(1, g);
                 cp_async_mbar_arrive_noinc(&ms.kv_full[st]);   // asynchronous: the thread does not wait for its copies
                 if (first) {
                     // Q rows of the new sequence -> swizzled K-major panels of Q buffer (pair & 1)
@@ -257,23 +246,26 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             }
             cp_async_wait_all();
         } else if (warp == 4) {
-            // =========================== MMA issue (one lane) ===========================
+            // =========================== QK issue (one lane) ===========================
+            // The two contractions are issued by two threads in two warps: one thread sustains one tcgen05.mma
+            // per ~57 cycles at these shapes, the tensor pipe one per ~41 (measured: 34 MMAs of a tile take 1950
+            // cycles from one thread, 1400 from two).  tcgen05.commit tracks the MMAs of the committing thread, which
+            // is exactly what each barrier needs: s_full / q_empty follow the QK stream, kv_empty / p_empty the PV
+            // stream (QK of a tile is complete before its softmax, hence before its PV).
             if (lane == 0) {
                 constexpr uint32_t IDESC_QK = make_idesc(MMA_M, N, false, false);
-                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
                 // descriptor bases; per-MMA descriptors differ only in the start address
                 const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                  // + stage
                 const uint64_t d_qk_a_rope = make_desc(smem_base + 4 * PANEL_BYTES, 16, 512, SWIZZLE_64B);   // + stage
                 const uint64_t d_qk_b = make_desc(smem_base + L::OFF_Q, 16, 1024, SWIZZLE_128B);       // + Q buffer
-                const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
-                const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, MMA_M * 16, SWIZZLE_NONE); // + buffer
-                Walker wq, wv;                                    // the QK stream runs ahead of the PV stream
-                wq.init(prefix, p.batch, t_begin);
-                wv = wq;
-                // S^T[128 tok x N] = K . Q^T for tile g
-                auto issue_qk = [&](int g) {
+                Walker wq; wq.init(prefix, p.batch, t_begin);
+                for (int g = 0; g < n_total; ++g) {
+                    // S^T[128 tok x N] = K . Q^T for tile g: the tile has landed, its S buffer has been read, its Q is in place
+                    const bool first = wq.seek(p, prefix, t_begin + g);
                     const int st = g % NS, sb = g & 1;
-                    TRACE(2, g);
+                    mbar_wait(&ms.kv_full[st], g / NS, abort_flag);
+                    mbar_wait(&ms.s_empty[sb], g / 2 - 1, abort_flag);
+                    if (first) mbar_wait(&ms.q_full[wq.pair & 1], wq.pair / 2, abort_flag);
                     fence_proxy_async();       // stage and Q were written by cp.async (generic proxy); the MMA reads through the async proxy
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_qk_a, st * STAGE_BYTES);
@@ -288,12 +280,22 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     umma_commit(&ms.s_full[sb]);
                     // last tile of this (CTA, sequence) pair: its Q buffer is free once these MMAs have run
                     if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit(&ms.q_empty[wq.pair & 1]);
-                    TRACE(3, g);
-                };
-                // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
-                auto issue_pv = [&](int g, bool first) {
+                }
+            }
+        } else if (warp == 5) {
+            // =========================== PV issue (one lane) ===========================
+            if (lane == 0) {
+                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
+                const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
+                const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, MMA_M * 16, SWIZZLE_NONE); // + buffer
+                Walker wv; wv.init(prefix, p.batch, t_begin);
+                for (int g = 0; g < n_total; ++g) {
+                    // O^T += V^T P^T over the tokens of tile g, four blocks of 128 dims, as soon as P(g) is published
+                    const bool first = wv.seek(p, prefix, t_begin + g);
                     const int st = g % NS, pb = g & 1;
-                    TRACE(4, g);
+                    mbar_wait(&ms.p_full[pb], g / 2, abort_flag);
+                    // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
+                    if (first && wv.pair > 0) mbar_wait(&ms.o_free, wv.pair - 1, abort_flag);
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
                     const uint64_t b0 = desc_advance(d_pv_b, pb * L::P_BUF_BYTES);
@@ -307,38 +309,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     }
                     umma_commit(&ms.kv_empty[st]);
                     umma_commit(&ms.p_empty[pb]);
-                    TRACE(5, g);
-                };
-                // Event driven: PV(g) as soon as P(g) is published (it frees the tile for the gather), else
-                // QK of the next tile as soon as it has landed, its S buffer is free and its Q is in place.
-                int nq = 0, nv = 0;
-                bool q_first = wq.seek(p, prefix, t_begin), v_first = wv.seek(p, prefix, t_begin);
-                long long t_idle = clock64();
-                uint32_t spins = 0;
-                while (nv < n_total) {
-                    bool pv_ready = nv < nq && mbar_try_nb(&ms.p_full[nv & 1], (uint32_t)(nv / 2) & 1u);
-                    // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
-                    if (pv_ready && v_first && wv.pair > 0) pv_ready = mbar_try_nb(&ms.o_free, (uint32_t)(wv.pair - 1) & 1u);
-                    bool qk_ready = !pv_ready && nq < n_total &&
-                                    mbar_try_nb(&ms.kv_full[nq % NS], (uint32_t)(nq / NS) & 1u) &&
-                                    mbar_try_nb(&ms.s_empty[nq & 1], (uint32_t)(nq / 2 - 1) & 1u);
-                    if (qk_ready && q_first) qk_ready = mbar_try_nb(&ms.q_full[wq.pair & 1], (uint32_t)(wq.pair / 2) & 1u);
-                    if (!pv_ready && !qk_ready && (++spins & 63u) == 0u) {
-                        if (spins == 64u) t_idle = clock64();
-                        if (*abort_flag || clock64() - t_idle > WAIT_LIMIT_CYCLES) {
-                            *abort_flag = 1;        // give up waiting; issue the rest regardless so that every commit still arrives
-                            if (nq < n_total) qk_ready = true; else pv_ready = true;
-                        }
-                    }
-                    if (pv_ready) {
-                        issue_pv(nv, v_first);
-                        ++nv; spins = 0;
-                        if (nv < n_total) v_first = wv.seek(p, prefix, t_begin + nv);
-                    } else if (qk_ready) {
-                        issue_qk(nq);
-                        ++nq; spins = 0;
-                        if (nq < n_total) q_first = wq.seek(p, prefix, t_begin + nq);
-                    }
                 }
             }
         } else {
@@ -390,7 +360,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     }
                 }
                 mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
-                if (tid == 0) TRACE(6, g);
                 tc_fence_after();
                 float s[N];
 #pragma unroll
@@ -412,9 +381,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 float xm = x[0];
 #pragma unroll
                 for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
-                if (tid == 0) TRACE(7, g);
                 const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
-                if (tid == 0) TRACE(8, g);
                 if (recenter) {
                     float mx[N];
 #pragma unroll
@@ -455,7 +422,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 }
                 // P(g) may overwrite its buffer once PV(g-2) has completed
                 mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
-                if (tid == 0) TRACE(9, g);
                 uint8_t* pbuf = smem + L::OFF_P + sb * L::P_BUF_BYTES;
 #pragma unroll
                 for (int c0 = 0; c0 < N; c0 += 16) {
@@ -479,12 +445,10 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 }
                 fence_proxy_async();
                 mbar_arrive(&ms.p_full[sb]);
-                if (tid == 0) TRACE(10, g);
 
                 if (last) {
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
                     mbar_wait(&ms.p_empty[sb], g / 2, abort_flag);
-                    if (tid == 0) TRACE(3, 63);
                     tc_fence_after();
                     reduce_cols(l_acc, false);
                     const bool whole = (t_begin <= wk.seq_t0) && (wk.seq_t1 <= t_end);
@@ -529,15 +493,13 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         if (whole) { if (p.out_lse) p.out_lse[(long long)wk.b * p.rows + row0 + tid] = lse; }
                         else p.part_lse[(long long)slot * p.rows + row0 + tid] = lse;
                     }
-                    if (tid == 0) TRACE(4, 63);
                 }
             }
         }
     }
 
     __syncthreads();
-    if (tid == 0) TRACE(5, 63);
-    if (tid == 0 && ms.abort_flag) atomicMax(status, (int)ST_TIMEOUT);
+    if (tid == 0 && ms.abort_flag) atomicOr(status, (int)ST_TIMEOUT);
     if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem, L::TMEM_COLS); }
 }
 
@@ -557,12 +519,6 @@ bool sm100_supported(const MlaParams& p) {
     const size_t need = sm100_rows_per_cta(p) == 32 ? smem_need<32>(p.batch) : smem_need<16>(p.batch);
     return need <= (size_t)sm100::SMEM_LIMIT;
 }
-
-#ifdef B200MLA_TRACE
-extern "C" int b200_mla_debug_set_trace(long long* ptr) {
-    return (int)cudaMemcpyToSymbol(sm100::g_trace, &ptr, sizeof(ptr));
-}
-#endif
 
 template <int N>
 static cudaError_t launch_n(const MlaParams& p, int* status, cudaStream_t stream) {

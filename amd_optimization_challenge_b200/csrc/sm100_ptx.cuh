@@ -10,8 +10,6 @@ namespace sm100 {
 
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // ~1 s: far beyond any legitimate wait of this kernel
 
-enum { ST_OK = 0, ST_TIMEOUT = 1 };
-
 // ----------------------------------------------------------------------------------------------
 // PTX wrappers
 // ----------------------------------------------------------------------------------------------

@@ -3,8 +3,9 @@ input generator (competitor_submissions/mi355x_reference/reference.py:40-154, 28
 
 Everything here is plain torch and runs on whatever device its inputs live on; it constructs
 inputs, it is not the decode path.  Differences from the reference, all opt-in through keyword
-arguments: random numbers are drawn on the CPU (the reference draws on a CUDA generator, whose
-bit stream cannot be reproduced without a GPU), the MXFP4 quantiser is implemented here (the
+arguments: random numbers are drawn on the CPU unless generator_device="cuda" is asked for (the
+reference draws on a CUDA generator, whose bit stream cannot be reproduced without a GPU), the
+MXFP4 quantiser is implemented here (the
 reference calls the AMD-only aiter op; the rounding rule is that of
 mxfp4-mm/submission_v3_self_contained.py:19-72), and the generator can also emit a page table,
 ragged lengths, more heads and the hybrid cache format.
@@ -123,28 +124,33 @@ def quantize_hybrid(kv_bf16: torch.Tensor):
 
 def generate_input(batchsize: int, qseqlen: int, kvseqlen: int, seed: int, *, num_heads: int = NUM_HEADS,
                    kv_lens=None, shuffle_pages: bool = False, sm_scale: float | None = None,
-                   formats=("bf16", "fp8", "mxfp4"), device="cuda"):
+                   formats=("bf16", "fp8", "mxfp4"), device="cuda", generator_device="cpu"):
     """Same contract as reference.generate_input (reference.py:288-346):
     returns (q, kv_data, qo_indptr, kv_indptr, config) with
       q          [batch*q_len, heads, 576] bf16 ~ N(0,1)
       kv_data    {"bf16": [T,1,576], "fp8": (e4m3fn [T,1,576], f32[1]),
                   "mxfp4": (u8 [T,1,288], u8 [T,18]), "hybrid": (see quantize_hybrid)}
       indptrs    int32 [batch+1]
-    q is drawn before kv from one seeded CPU generator, as in the reference.
+    q is drawn before kv from one seeded generator, the reference's order.  With the default
+    generator_device="cpu" the draw and the quantisers run on the host (the same bytes with or without a
+    GPU, which is what the oracle comparisons need) and therefore differ from the reference's tensors for
+    equal seeds; generator_device="cuda" draws from torch.Generator(device="cuda") exactly as the
+    reference does (reference.py:299-315) and quantises on the GPU.
 
     Extensions: `kv_lens` (ragged lengths; kvseqlen is then only recorded in config),
     `shuffle_pages` (page_size-1 page table: config["kv_indices"] is a seeded permutation of the
     slot pool and the cache rows are stored in slot order), `num_heads`, `formats`.
     """
-    gen = torch.Generator(device="cpu")
+    gen = torch.Generator(device=generator_device)
     gen.manual_seed(seed)
+    gdev = torch.device(generator_device)
     lens = [kvseqlen] * batchsize if kv_lens is None else [int(v) for v in kv_lens]
     assert len(lens) == batchsize
     total_q = batchsize * qseqlen
     total_kv = sum(lens)
 
-    q = torch.randn((total_q, num_heads, QK_HEAD_DIM), dtype=torch.bfloat16, generator=gen)
-    kv_logical = torch.randn((total_kv, NUM_KV_HEADS, QK_HEAD_DIM), dtype=torch.bfloat16, generator=gen)
+    q = torch.randn((total_q, num_heads, QK_HEAD_DIM), dtype=torch.bfloat16, generator=gen, device=gdev)
+    kv_logical = torch.randn((total_kv, NUM_KV_HEADS, QK_HEAD_DIM), dtype=torch.bfloat16, generator=gen, device=gdev)
 
     config = {
         "batch_size": batchsize, "num_heads": num_heads, "num_kv_heads": NUM_KV_HEADS,
@@ -154,7 +160,7 @@ def generate_input(batchsize: int, qseqlen: int, kvseqlen: int, seed: int, *, nu
         "total_kv": total_kv,
     }
     if shuffle_pages:
-        perm = torch.randperm(total_kv, generator=gen)          # logical token i lives in slot perm[i]
+        perm = torch.randperm(total_kv, generator=gen, device=gdev)   # logical token i lives in slot perm[i]
         kv_store = torch.empty_like(kv_logical)
         kv_store[perm] = kv_logical
         config["kv_indices"] = perm.to(torch.int32).to(device)

@@ -14,6 +14,8 @@ What the reference's router chooses from a (batch, kv_len) table is chosen here 
     config["page_size"], config["kv_page_indptr"]     pages larger than one token
     config["sm_scale"]   softmax scale (never hard-coded)
     config["impl"]       "auto" | "generic" | "tcgen05"
+    config["check_status"]  True: wait for the call and raise if a device-side wait expired or the page
+                         table named a slot outside the cache (costs one host synchronisation)
 
 A q tensor that already is float8_e4m3fn is used as is with config["q_scale"].
 Scratch (partials, quantised Q) is cached per (device, shape) like the reference's buffer caches
@@ -56,9 +58,54 @@ def _workspace(device, batch: int, heads: int, q_len: int) -> torch.Tensor:
         with torch.cuda.device(device):
             n = lib.b200_mla_workspace_bytes(batch, heads, q_len)
         ws = torch.empty(n, dtype=torch.uint8, device=device)
-        ws[:256].zero_()                      # kernel status word (sticky; 0 = no device-side wait ever expired)
+        with torch.cuda.device(device):       # sticky status word: zero once per buffer
+            check(lib.b200_mla_reset_status(ws.data_ptr(), _stream(device)), "b200_mla_reset_status")
         _workspace_cache[key] = ws
     return ws
+
+
+def read_status(device=None, batch: int | None = None, heads: int | None = None, q_len: int = 1) -> int:
+    """Sticky device-side status bits (`_cabi.STATUS_TIMEOUT`, `_cabi.STATUS_BAD_PAGE`) ORed over every
+    cached workspace of `device`, or of the one workspace of the given shape.  Synchronises the stream."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = torch.zeros(1, dtype=torch.int32, device=device)
+    bits = 0
+    for key, ws in list(_workspace_cache.items()):
+        if key[0] != device.index or (batch is not None and key[1:] != (batch, heads, q_len)):
+            continue
+        with torch.cuda.device(device):
+            check(lib.b200_mla_read_status(ws.data_ptr(), word.data_ptr(), _stream(device)), "b200_mla_read_status")
+        bits |= int(word.item())
+    return bits
+
+
+def _check_index_tensor(name: str, t, device, min_numel: int = 0):
+    """Page-table style argument: the kernels read it as dense int32 on the decode device.  Anything else
+    (int64 from torch.arange, a CPU tensor, a strided view) would be misread on the GPU, so it is refused here."""
+    if t is None:
+        return
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if t.dtype != torch.int32:
+        raise TypeError(f"{name} must be int32, got {t.dtype}")
+    if t.device != device:
+        raise ValueError(f"{name} is on {t.device}, the decode runs on {device}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if t.numel() < min_numel:
+        raise ValueError(f"{name} has {t.numel()} entries, the call needs at least {min_numel}")
+
+
+def _check_plane(name: str, t, device, dtype=None):
+    """Cache plane / scale argument: on the decode device, unit stride along the row (and the dtype, if given)."""
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if t.device != device:
+        raise ValueError(f"{name} is on {t.device}, the decode runs on {device}")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if t.dim() > 0 and t.stride(-1) != 1 and t.shape[-1] != 1:
+        raise ValueError(f"{name} must have unit stride along its last dimension")
 
 
 def quantize_q_fp8(q: torch.Tensor):
@@ -118,9 +165,19 @@ def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Te
     rows_total, heads, d = q.shape
     if d != QK_DIM:
         raise ValueError(f"q last dim must be {QK_DIM}")
+    _check_index_tensor("kv_indptr", kv_indptr, dev, 2)
     batch = kv_indptr.numel() - 1
     if rows_total != batch * q_len:
         raise ValueError("q rows must equal batch * q_len")
+    if page_size < 1:
+        raise ValueError("page_size must be >= 1")
+    _check_index_tensor("kv_indices", kv_indices, dev,
+                        -(-int(total_kv_hint) // page_size) if (total_kv_hint and page_size == 1) else 0)
+    _check_index_tensor("kv_page_indptr", kv_page_indptr, dev, batch + 1)
+    _check_index_tensor("kv_pos_offset", kv_pos_offset, dev, batch)
+    _check_index_tensor("kv_total_len", kv_total_len, dev, batch)
+    for i, t in enumerate(kv):
+        _check_plane(f"kv[{i}]", t, dev)
     a = DecodeArgs()
     a.batch, a.heads, a.q_len = batch, heads, q_len
     a.causal, a.page_size, a.impl = int(causal), page_size, _IMPLS[impl]
@@ -129,6 +186,9 @@ def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Te
     if q.dtype == torch.bfloat16 and q_cast:
         if q_scale is None:
             raise ValueError("q_cast needs the partial maxima of q_amax_parts(q) as q_scale")
+        _check_plane("q_scale", q_scale, dev, torch.int32)
+        if q_scale.numel() < _cabi.Q_AMAX_PARTS:
+            raise ValueError(f"q_scale must hold the {_cabi.Q_AMAX_PARTS} partial maxima of q_amax_parts(q)")
         a.q_format = _cabi.Q_BF16_CAST_E4M3
         a.q_scale = q_scale.data_ptr()
     elif q.dtype == torch.bfloat16:
@@ -137,6 +197,7 @@ def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Te
         a.q_format = _cabi.Q_E4M3
         if q_scale is None:
             raise ValueError("e4m3 Q needs q_scale")
+        _check_plane("q_scale", q_scale, dev, torch.float32)
         a.q_scale = q_scale.data_ptr()
     else:
         raise ValueError(f"unsupported q dtype {q.dtype}")
@@ -149,6 +210,7 @@ def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Te
     if kv_format == "fp8":
         codes, scale = kv
         codes = _u8(codes).reshape(-1, QK_DIM)
+        _check_plane("kv scale", scale, dev, torch.float32)
         a.kv_scale = scale.data_ptr()
     elif kv_format == "mxfp4":
         codes, bs = kv
@@ -161,6 +223,7 @@ def mla_decode(q: torch.Tensor, q_scale, kv_format: str, kv, kv_indptr: torch.Te
         codes = _u8(codes).reshape(-1, V_DIM // 2)
         bs = _u8(bs)
         rope = _u8(rope).reshape(-1, QK_DIM - V_DIM)
+        _check_plane("kv rope scale", scale, dev, torch.float32)
         a.kv_block_scales, a.kv_block_scales_stride = bs.data_ptr(), bs.stride(0)
         a.kv_rope, a.kv_rope_stride = rope.data_ptr(), rope.stride(0)
         a.kv_scale = scale.data_ptr()
@@ -250,9 +313,17 @@ def custom_kernel(data):
         hint = int(sum(config["kv_lens"]))
     else:
         hint = int(config["batch_size"]) * int(config["kv_seq_len"])
-    return mla_decode(
+    out = mla_decode(
         q, q_scale, kv_format, kv_data[kv_format], kv_indptr,
         sm_scale=config["sm_scale"], q_len=q_len, kv_indices=config.get("kv_indices"),
         page_size=int(config.get("page_size", 1)), kv_page_indptr=config.get("kv_page_indptr"),
         causal=bool(config.get("causal", True)), total_kv_hint=hint, impl=config.get("impl", "auto"),
         max_ctas=int(config.get("max_ctas", 0)), q_cast=q_cast)
+    if config.get("check_status"):
+        bits = read_status(out.device, kv_indptr.numel() - 1, q.shape[1], q_len)
+        if bits:
+            what = [n for b, n in ((_cabi.STATUS_TIMEOUT, "a device-side wait expired (the output is not valid)"),
+                                   (_cabi.STATUS_BAD_PAGE, "the page table named a slot outside the cache (read as zeros)"))
+                    if bits & b]
+            raise RuntimeError(f"mla decode status {bits}: " + "; ".join(what) + " (the word is sticky for this workspace)")
+    return out

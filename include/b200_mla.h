@@ -63,7 +63,7 @@ typedef struct {
     /* ---- problem ---- */
     int32_t batch;            /* sequences */
     int32_t heads;            /* query heads sharing the single latent KV head; multiple of 16 */
-    int32_t q_len;            /* queries per sequence (1, or 2..4 for speculative decode) */
+    int32_t q_len;            /* queries per sequence (1, or 2..8 for speculative decode) */
     int32_t q_format;         /* b200_mla_q_format */
     int32_t kv_format;        /* b200_mla_kv_format */
     int32_t causal;           /* non-zero: query j sees key position p iff p <= total_len - q_len + j */
@@ -82,12 +82,17 @@ typedef struct {
     /* ---- KV cache planes (device) ---- */
     const void *kv_codes;     /* e4m3: [slots,576]; mxfp4: [slots,288]; hybrid: latent [slots,256] */
     int64_t kv_codes_stride;  /* bytes between slots; multiple of 16 */
-    const void *kv_block_scales;   /* E8M0 bytes (mxfp4: >=18 per slot, hybrid: >=16); NULL for e4m3 */
+    const void *kv_block_scales;   /* E8M0 bytes (mxfp4: >=18 per slot, hybrid: >=16); NULL for e4m3.  The tcgen05
+                                    * kernels fetch a slot's bytes as the aligned 8-byte words around them: up to 7
+                                    * bytes before the first and after the last row of the plane may be read
+                                    * (never used), so the plane must not end flush against unmapped memory */
     int64_t kv_block_scales_stride;/* bytes between slots (the reference pads this plane, reference.py:125-148) */
     const void *kv_rope;      /* hybrid only: [slots,64] e4m3fn */
     int64_t kv_rope_stride;   /* bytes between slots; multiple of 16 */
     const float *kv_scale;    /* device fp32[1]: per-tensor scale of the e4m3 codes (e4m3: whole row, hybrid: rope) */
-    int64_t num_slots;        /* rows in the cache planes (bounds for kv_indices) */
+    int64_t num_slots;        /* rows in the cache planes, > 0.  Every slot the page table yields is checked against
+                               * it on the device: a slot outside [0, num_slots) is not read (the key counts as a
+                               * row of zeros) and sets B200_MLA_STATUS_BAD_PAGE */
 
     /* ---- page table ---- */
     const int32_t *kv_indptr;     /* device int32[batch+1], token offsets (task.py:14) */
@@ -107,7 +112,9 @@ typedef struct {
     float *out_lse;           /* optional: fp32 natural-log LSE [batch*q_len, heads]; -inf for an empty key set */
 
     /* ---- scratch ---- */
-    void *workspace;          /* device, 256-byte aligned */
+    void *workspace;          /* device, 256-byte aligned.  Its first 256 bytes hold the sticky status word and must
+                               * be zero before the first call that uses a fresh buffer (b200_mla_reset_status,
+                               * or any memset); later calls leave them alone */
     int64_t workspace_bytes;  /* >= b200_mla_workspace_bytes() */
 } b200_mla_decode_args;
 
@@ -188,6 +195,23 @@ int32_t b200_mla_q_amax(const void *x_bf16, int64_t n, uint32_t *parts_out, void
  */
 #define B200_MLA_STATIC_WORKSPACE_BYTES (16u << 20)
 int32_t b200_mla_decode_static(const b200_mla_decode_args *args, void *stream);
+
+/*
+ * Device-side status of the decode calls that used `workspace` (no counterpart in the reference: AITER's kernels
+ * report nothing, mixed-mla/submission.py:626-644 returns whatever they wrote).  The kernels OR bits into the first
+ * word of the workspace and never clear them:
+ *   B200_MLA_STATUS_TIMEOUT   a bounded device-side wait expired; the outputs of that call are not valid
+ *   B200_MLA_STATUS_BAD_PAGE  kv_indptr / kv_indices named a slot outside [0, num_slots); that key was replaced
+ *                             by a row of zeros, nothing outside the cache planes was read
+ * b200_mla_read_status enqueues one 4-byte copy of the word into `out` (device, pinned or pageable host memory) on
+ * `stream`; the caller decides whether and when to wait for it.  b200_mla_reset_status enqueues the zeroing of the
+ * word (and of the rest of the 256-byte header); call it once on a fresh workspace.  workspace == NULL addresses
+ * the built-in scratch of b200_mla_decode_static on the current device.
+ */
+#define B200_MLA_STATUS_TIMEOUT 1
+#define B200_MLA_STATUS_BAD_PAGE 2
+int32_t b200_mla_read_status(const void *workspace, int32_t *out, void *stream);
+int32_t b200_mla_reset_status(void *workspace, void *stream);
 
 /*
  * Profiling aid (no counterpart in the reference, whose harness times whole calls, eval.py:225-261):

@@ -2,7 +2,7 @@
 
 Run once, by hand, in a container that has the reference checkout mounted:
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference      (the path is required)
 
 What runs (paths relative to the reference project root):
 
@@ -16,6 +16,10 @@ What runs (paths relative to the reference project root):
 * `triton_mla_decode_fp8` (mixed-mla/triton_fp8_decode.py:233-280; bf16 Q x FP8 KV, split-KV
   stage 1 + LSE reduce) and `triton_mla_decode_mxfp4` (mixed-mla/triton_mla_mxfp4.py:234-290;
   bf16 Q x MXFP4 KV) under the interpreter, on small ragged seeded inputs.
+* One FP8-Q x FP8-KV decode in a single fixture: the same Q through the reference's `quantize_fp8`,
+  then `triton_mla_decode_fp8` on the e4m3 values of Q (exact in bf16) with the per-tensor Q scale
+  folded into the module's softmax-scale constant for that one call - i.e. quantiser + decode as
+  `ref_kernel` chains them (reference.py:349-369), evaluated by the reference's own Triton kernels.
 
 The fixtures store the exact input bytes and the reference's outputs; nothing else in the
 repository reads the reference checkout.  The tests that consume them are
@@ -228,6 +232,19 @@ def main(ref_root: str):
     out["dec_fp8_scale"] = s8.numpy()
     out["dec_fp8_out_bf16bits"] = bf16_bits(o8)
 
+    # FP8 Q: quantiser + decode in one fixture.  The e4m3 codes of Q are exact in bf16; their per-tensor
+    # scale multiplies every score, so it rides on the softmax scale the kernel reads from its module.
+    q8, qs8 = ref.quantize_fp8(q)
+    sm_saved = ref8.SM_SCALE
+    ref8.SM_SCALE = sm_saved * float(qs8)
+    try:
+        o88 = ref8.triton_mla_decode_fp8(q8.to(torch.float32).to(torch.bfloat16), kv8, s8, kv_indptr, cfg).clone()
+    finally:
+        ref8.SM_SCALE = sm_saved
+    out["dec_q8_codes"] = q8.view(torch.uint8).numpy()
+    out["dec_q8_scale"] = qs8.numpy()
+    out["dec_fp8q_out_bf16bits"] = bf16_bits(o88)
+
     # MXFP4 bytes for the same rows, produced by the reference quantiser (row blocks of 16)
     kv2 = kv.reshape(T, 576).to(torch.float32)
     c4 = torch.zeros(T, 288, dtype=torch.uint8)
@@ -250,4 +267,6 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+    main(sys.argv[1])

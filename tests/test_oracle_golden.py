@@ -71,6 +71,18 @@ def test_decode_matches_reference_fp8_kernel(golden):
     _bf16_ulp_close(o, bf16_from_bits(golden["dec_fp8_out_bf16bits"]))
 
 
+def test_fp8_q_decode_matches_reference_chain(golden):
+    """Quantiser + decode in one fixture: the reference's quantize_fp8 on Q, then its Triton FP8 kernel on
+    the e4m3 values with the Q scale folded into the softmax scale."""
+    q = bf16_from_bits(golden["dec_q_bf16bits"])
+    codes, scale = mo.quantize_fp8_per_tensor(q)
+    assert np.array_equal(codes.numpy(), golden["dec_q8_codes"])
+    assert float(scale) == float(golden["dec_q8_scale"][0])
+    kv = (torch.from_numpy(golden["dec_fp8_codes"]).reshape(-1, 576), torch.from_numpy(golden["dec_fp8_scale"]))
+    o = mo.decode_from_data(codes, scale, "fp8", kv, golden["dec_kv_indptr"], None, SM)
+    _bf16_ulp_close(o, bf16_from_bits(golden["dec_fp8q_out_bf16bits"]))
+
+
 def test_decode_matches_reference_mxfp4_kernel(golden):
     q = bf16_from_bits(golden["dec_q_bf16bits"])
     kv = (torch.from_numpy(golden["dec_mx_codes"]), torch.from_numpy(golden["dec_mx_scales"]))
