@@ -38,6 +38,7 @@ struct MlaParams {
     const uint8_t* kv_bs; long long kv_bs_stride;
     const uint8_t* kv_rope; long long kv_rope_stride;
     const float* kv_scale; long long num_slots;
+    long long total_kv_hint;            // > 0: the host's bound on kv_indptr[batch]; kv_indices holds at least that many tokens' ids
     const int* kv_indptr; const int* kv_indices; const int* kv_page_indptr;
     const int* kv_pos_offset; const int* kv_total_len;
 
@@ -157,7 +158,8 @@ struct Walker {
     int pair;                               // (CTA, sequence) pairs started so far, minus one
     __device__ __forceinline__ void init(const int* prefix, int batch, int t_begin) {
         b = seq_of_tile(prefix, batch, t_begin) - 1;
-        seq_t1 = -1;
+        seq_t0 = 0; seq_t1 = -1;
+        seq_base = seq_len = page_base = pos_off = tot_len = 0;
         pair = -1;
     }
     // Make the walker describe the sequence that owns global tile t (t only grows between calls).

@@ -16,9 +16,8 @@
 // waits until the epilogue has read O out of TMEM).
 //
 // Roles:  warps 0-3  softmax / correction / epilogue (one TMEM lane = one token / one output dim per thread)
-//         warp  4    tcgen05.mma issue of the QK stream (one lane), TMEM allocation
-//         warp  5    tcgen05.mma issue of the PV stream (one lane)
-//         warps 6..  paged gather: 16-byte cp.async of cache rows (and of Q) through the page table
+//         warp  4    tcgen05.mma issue (one lane, event driven), TMEM allocation
+//         warps 5..  paged gather: 16-byte cp.async of cache rows (and of Q) through the page table
 //                    straight into the 128B-swizzled UMMA layout, completion signalled on an mbarrier.
 // Movers measured on B200 for shuffled 576-byte rows, device-wide, one CTA per SM:
 //         16-byte cp.async (LSU)                       3.5 - 4.4 TB/s, lands directly in operand layout
@@ -39,6 +38,7 @@ namespace sm100 {
 
 constexpr int MMA_M = 128;                // rows of every MMA: tokens for QK, output dims for PV; S and P span MMA_M rows
 constexpr int NS_MAX = 3;
+constexpr int SLOT_RING = 8;              // tiles whose page ids can be in flight / in use at once
 constexpr int SMEM_LIMIT = 232448;        // opt-in shared memory per CTA
 constexpr float RECENTER = 4.0f;          // log2 units
 constexpr float P_SCALE_LOG2 = 4.0f;      // probabilities are stored multiplied by 2^4
@@ -58,10 +58,9 @@ struct Layout {
     static constexpr int ROPE_PANEL_BYTES = TILE * 64;           // dims 512..575: 64-byte rows, 64B swizzle
     static constexpr int STAGE_BYTES = 4 * PANEL_BYTES + ROPE_PANEL_BYTES;
     static constexpr int NPANEL = 5;                             // Q keeps five 128-byte-wide panels
-    static constexpr int PRODUCER_WARPS = (N == 16) ? 10 : 2;    // 512 threads at 128 registers; N = 32 needs the registers
+    static constexpr int PRODUCER_WARPS = (N == 16) ? 9 : 2;     // N = 16: 288 = 8 x 36 threads, one 16-byte column and one row phase each; N = 32 needs the registers
     static constexpr int PRODUCERS = 32 * PRODUCER_WARPS;
-    static constexpr int FIRST_PRODUCER = 192;                     // warps 0-3 softmax, 4 QK issue, 5 PV issue
-    static constexpr int THREADS = FIRST_PRODUCER + PRODUCERS;
+    static constexpr int THREADS = 160 + PRODUCERS;
     static constexpr int Q_PANEL_BYTES = N * 128;
     static constexpr int Q_BYTES = NPANEL * Q_PANEL_BYTES;        // one Q buffer (two of them: next sequence's Q loads early)
     static constexpr int P_CHUNKS = 2 * N / 16;                  // 16-column chunks of [hi | lo]
@@ -80,7 +79,8 @@ struct Misc {
     uint32_t tmem_base;
     int abort_flag;
     unsigned int q_amax;         // block_q_scale's word
-    int slot[NS_MAX][MMA_M];
+    uint64_t slot_full[SLOT_RING];
+    int slot[SLOT_RING][MMA_M];  // page ids of the tiles g .. g + NS, fetched by 4-byte cp.async
     float red[4][32];            // cross-warp exchange (max / sum), 32 = max N
 };
 
@@ -100,6 +100,14 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     const unsigned int q_amax_local = block_q_amax_begin(p.q_amax_parts, p.q_cast);   // loads in flight during the prologue
     const float kv_sc = __ldg(p.kv_scale);       // issued here, first used by the softmax role: no role waits for it at its start
 
+    // The page ids this CTA will walk lie near w/G of the table: pull that neighbourhood into L2 while kv_indptr is being
+    // read and scanned, so that the first dependent page-table read is not a cold DRAM access.
+    if (p.kv_indices != nullptr && p.total_kv_hint > 0 && tid < 64) {
+        const long long n_ids = p.total_kv_hint / p.page_size, per = n_ids / G;
+        const long long lo = max((long long)w * per - 256, 0LL) & ~31LL, hi = min((long long)(w + 1) * per + 256, n_ids);
+        for (long long i = lo + tid * 32; i < hi; i += 64 * 32)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kv_indices + i));
+    }
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], PRODUCERS); mbar_init(&ms.kv_empty[i], 1); }
         for (int i = 0; i < 2; ++i) {
@@ -107,6 +115,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             mbar_init(&ms.p_full[i], 128); mbar_init(&ms.p_empty[i], 1);
             mbar_init(&ms.q_full[i], PRODUCERS); mbar_init(&ms.q_empty[i], 1);
         }
+        for (int i = 0; i < SLOT_RING; ++i) mbar_init(&ms.slot_full[i], PRODUCERS);
         mbar_init(&ms.o_free, 128);
         ms.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -126,27 +135,48 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
-        if (warp >= 6) {
+        if (warp >= 5) {
             // =========================== gather ===========================
-            // One stage = 128 tokens x 36 sixteen-byte columns.  Consecutive threads take consecutive
+            // One stage = TILE tokens x 36 sixteen-byte columns.  Consecutive threads take consecutive
             // columns, so a warp instruction reads 512 contiguous bytes of (at most two) rows.
-            const int pt = tid - L::FIRST_PRODUCER;
+            const int pt = tid - 160;
             Walker wk; wk.init(prefix, p.batch, t_begin);
-            Walker wn = wk;                                       // one tile ahead, for the page-table prefetch
-            // thread pt looks up the page table for tokens pt, pt + PRODUCERS, ... of a tile (-1 past the end)
-            constexpr int SLOTS_PER_THREAD = (TILE + PRODUCERS - 1) / PRODUCERS;
-            int my_slot[SLOTS_PER_THREAD];
-            auto slots_for = [&](int g) {
-                if (g < n_total) wn.seek(p, prefix, t_begin + g);
-#pragma unroll
-                for (int k = 0; k < SLOTS_PER_THREAD; ++k) {
-                    const int tok = pt + k * PRODUCERS;
-                    const int pos = (t_begin + g - wn.seq_t0) * TILE + tok;
-                    my_slot[k] = (g < n_total && tok < TILE && pos < wn.seq_len)
-                                     ? (int)slot_of(p, wn.b, wn.seq_base, wn.page_base, pos) : -1;
+            Walker wn = wk;                                       // NS tiles ahead, for the page-table prefetch
+            const bool paged = p.kv_indices != nullptr;
+            // Page ids of tile g -> ring entry g % SLOT_RING by 4-byte cp.async, NS tiles before the tile's rows are
+            // requested, completion on the entry's mbarrier (no registers held, no barrier among the gather threads).
+            // An entry is rewritten SLOT_RING tiles later; a thread that prefetches for tile g + NS has passed the
+            // kv_empty wait of tile g, so every other thread has at least issued tile g - NS and reads entries
+            // g - NS + 1 .. g at most: no overlap with entry g + NS as long as SLOT_RING > 2 NS.
+            static_assert(SLOT_RING > 2 * NS, "page-id ring");
+            auto prefetch_ids = [&](int g) {
+                if (!paged || g >= n_total) return;
+                wn.seek(p, prefix, t_begin + g);
+                const int pos0 = (t_begin + g - wn.seq_t0) * TILE;
+                for (int tok = pt; tok < TILE; tok += PRODUCERS) {
+                    const int pos = pos0 + tok;
+                    const bool ok = pos < wn.seq_len;
+                    const int pg = p.page_size == 1 ? pos : pos / p.page_size;
+                    cp_async4(smem_u32(&ms.slot[g % SLOT_RING][tok]), p.kv_indices + (ok ? wn.page_base + pg : 0), ok ? 4u : 0u);
                 }
+                cp_async_mbar_arrive_noinc(&ms.slot_full[g % SLOT_RING]);
             };
-            slots_for(0);
+            // cache slot of token `tok` of tile g (wk describes its sequence), -1 past the end of the sequence or when
+            // the page table points outside the cache planes (reported through the status word, the row reads as zeros)
+            auto slot_at = [&](int g, int pos0, int tok) -> int {
+                const int pos = pos0 + tok;
+                if (pos >= wk.seq_len) return -1;
+                long long sl;
+                if (!paged) sl = (long long)wk.seq_base + pos;
+                else {
+                    const int id = ms.slot[g % SLOT_RING][tok];
+                    sl = p.page_size == 1 ? (long long)id : (long long)id * p.page_size + (pos % p.page_size);
+                }
+                if (sl < 0 || sl >= p.num_slots) { atomicOr(p.status, (int)ST_BAD_PAGE); return -1; }
+                return (int)sl;
+            };
+#pragma unroll 1
+            for (int g = 0; g < NS; ++g) prefetch_ids(g);
             for (int g = 0; g < n_total; ++g) {
                 const int st = g % NS;
                 const bool first = wk.seek(p, prefix, t_begin + g);
@@ -168,36 +198,52 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         qv[Q_PRELOAD ? k : 0] = i < N * 72 ? __ldg(q_src(i)) : make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
+                const int pos0 = (t_begin + g - wk.seq_t0) * TILE;
+                if (paged) mbar_wait(&ms.slot_full[g % SLOT_RING], g / SLOT_RING, abort_flag);
                 mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
-#pragma unroll
-                for (int k = 0; k < SLOTS_PER_THREAD; ++k)
-                    if (pt + k * PRODUCERS < TILE) ms.slot[st][pt + k * PRODUCERS] = my_slot[k];
-                named_bar_sync(2, PRODUCERS);                   // slots of this tile visible to every gather thread
-                slots_for(g + 1);
                 const uint32_t stage_addr = smem_base + st * STAGE_BYTES;
-                // Slots first, then the copies, if possible for the whole tile at once: a shared-memory load that sits
-                // between copy instructions waits behind them in the load/store unit, and the copies after it wait for
-                // the load (measured in isolation: 4.1 TB/s with two batches per tile, 5.4 TB/s with one).
-                constexpr int PER_TILE = (TILE * 36 + PRODUCERS - 1) / PRODUCERS;
-                constexpr int BATCH = PER_TILE < 16 ? PER_TILE : 16;
-                for (int id0 = pt; id0 < TILE * 36; id0 += BATCH * PRODUCERS) {
-                    int sl[BATCH];
+                // Slots first, then the copies, for the whole tile at once: a shared-memory load that sits between copy
+                // instructions waits behind them in the load/store unit, and the copies after it wait for the load
+                // (measured in isolation: 4.1 TB/s with two batches per tile, 5.4 TB/s with one).
+                if constexpr (PRODUCERS % 36 == 0 && (PRODUCERS / 36) == 8) {
+                    // thread = (16-byte column c, row phase r): tokens r, r + 8, ...; the swizzle term of the destination
+                    // depends on the token only through r, so source and destination advance by constants
+                    constexpr int PER = TILE / 8;
+                    const int c = pt % 36, r = pt / 36;
+                    const uint32_t dst0 = c < 32 ? stage_addr + (c >> 3) * PANEL_BYTES + r * 128 + (((c & 7) ^ r) << 4)
+                                                 : stage_addr + 4 * PANEL_BYTES + r * 64 + (((c - 32) ^ ((r >> 1) & 3)) << 4);
+                    const uint32_t dstep = c < 32 ? 1024u : 512u;
+                    const uint8_t* src0 = p.kv_codes + c * 16;
+                    int sl[PER];
 #pragma unroll
-                    for (int u = 0; u < BATCH; ++u) {
-                        const int id = id0 + u * PRODUCERS;
-                        sl[u] = id < TILE * 36 ? ms.slot[st][id / 36] : -2;
-                    }
+                    for (int i = 0; i < PER; ++i) sl[i] = slot_at(g, pos0, r + 8 * i);
+                    prefetch_ids(g + NS);
 #pragma unroll
-                    for (int u = 0; u < BATCH; ++u) {
-                        const int id = id0 + u * PRODUCERS;
-                        if (sl[u] != -2) {
-                            const int tok = id / 36, c = id - tok * 36;
-                            const uint8_t* src = p.kv_codes + (long long)(sl[u] < 0 ? 0 : sl[u]) * p.kv_codes_stride + c * 16;
-                            const uint32_t dst = c < 32 ? stage_addr + (c >> 3) * PANEL_BYTES + tok * 128 + (((c & 7) ^ (tok & 7)) << 4)
-                                                        : stage_addr + 4 * PANEL_BYTES + tok * 64 + (((c - 32) ^ ((tok >> 1) & 3)) << 4);
-                            cp_async16(dst, src, sl[u] < 0 ? 0u : 16u);     // rows past the end of the sequence: zero fill
+                    for (int i = 0; i < PER; ++i)
+                        cp_async16(dst0 + i * dstep, src0 + (long long)max(sl[i], 0) * p.kv_codes_stride, sl[i] < 0 ? 0u : 16u);
+                } else {
+                    constexpr int PER_TILE = (TILE * 36 + PRODUCERS - 1) / PRODUCERS;
+                    constexpr int BATCH = PER_TILE < 16 ? PER_TILE : 16;
+                    for (int id0 = pt; id0 < TILE * 36; id0 += BATCH * PRODUCERS) {
+                        int sl[BATCH];
+#pragma unroll
+                        for (int u = 0; u < BATCH; ++u) {
+                            const int id = id0 + u * PRODUCERS;
+                            sl[u] = id < TILE * 36 ? slot_at(g, pos0, id / 36) : -2;
+                        }
+#pragma unroll
+                        for (int u = 0; u < BATCH; ++u) {
+                            const int id = id0 + u * PRODUCERS;
+                            if (sl[u] != -2) {
+                                const int tok = id / 36, c = id - tok * 36;
+                                const uint8_t* src = p.kv_codes + (long long)(sl[u] < 0 ? 0 : sl[u]) * p.kv_codes_stride + c * 16;
+                                const uint32_t dst = c < 32 ? stage_addr + (c >> 3) * PANEL_BYTES + tok * 128 + (((c & 7) ^ (tok & 7)) << 4)
+                                                            : stage_addr + 4 * PANEL_BYTES + tok * 64 + (((c - 32) ^ ((tok >> 1) & 3)) << 4);
+                                cp_async16(dst, src, sl[u] < 0 ? 0u : 16u);     // rows past the end of the sequence: zero fill
+                            }
                         }
                     }
+                    prefetch_ids(g + NS);
                 }
                 cp_async_mbar_arrive_noinc(&ms.kv_full[st]);   // asynchronous: the thread does not wait for its copies
                 if (first) {
@@ -246,26 +292,22 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             }
             cp_async_wait_all();
         } else if (warp == 4) {
-            // =========================== QK issue (one lane) ===========================
-            // The two contractions are issued by two threads in two warps: one thread sustains one tcgen05.mma
-            // per ~57 cycles at these shapes, the tensor pipe one per ~41 (measured: 34 MMAs of a tile take 1950
-            // cycles from one thread, 1400 from two).  tcgen05.commit tracks the MMAs of the committing thread, which
-            // is exactly what each barrier needs: s_full / q_empty follow the QK stream, kv_empty / p_empty the PV
-            // stream (QK of a tile is complete before its softmax, hence before its PV).
-            if (lane == 0) {
+            // =========================== MMA issue (whole warp, one elected lane per instruction) ===========================
+            {
                 constexpr uint32_t IDESC_QK = make_idesc(MMA_M, N, false, false);
+                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
                 // descriptor bases; per-MMA descriptors differ only in the start address
                 const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                  // + stage
                 const uint64_t d_qk_a_rope = make_desc(smem_base + 4 * PANEL_BYTES, 16, 512, SWIZZLE_64B);   // + stage
                 const uint64_t d_qk_b = make_desc(smem_base + L::OFF_Q, 16, 1024, SWIZZLE_128B);       // + Q buffer
-                Walker wq; wq.init(prefix, p.batch, t_begin);
-                for (int g = 0; g < n_total; ++g) {
-                    // S^T[128 tok x N] = K . Q^T for tile g: the tile has landed, its S buffer has been read, its Q is in place
-                    const bool first = wq.seek(p, prefix, t_begin + g);
+                const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
+                const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, MMA_M * 16, SWIZZLE_NONE); // + buffer
+                Walker wq, wv;                                    // the QK stream runs ahead of the PV stream
+                wq.init(prefix, p.batch, t_begin);
+                wv = wq;
+                // S^T[128 tok x N] = K . Q^T for tile g
+                auto issue_qk = [&](int g) {
                     const int st = g % NS, sb = g & 1;
-                    mbar_wait(&ms.kv_full[st], g / NS, abort_flag);
-                    mbar_wait(&ms.s_empty[sb], g / 2 - 1, abort_flag);
-                    if (first) mbar_wait(&ms.q_full[wq.pair & 1], wq.pair / 2, abort_flag);
                     fence_proxy_async();       // stage and Q were written by cp.async (generic proxy); the MMA reads through the async proxy
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_qk_a, st * STAGE_BYTES);
@@ -274,28 +316,16 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     for (int k = 0; k < 18; ++k) {
                         const uint64_t a = k < 16 ? desc_advance(a0, (k >> 2) * PANEL_BYTES + (k & 3) * 32)
                                                   : desc_advance(d_qk_a_rope, st * STAGE_BYTES + (k & 1) * 32);
-                        umma_f8(tmem + L::TMEM_S + sb * N, a,
+                        umma_f8_elect(tmem + L::TMEM_S + sb * N, a,
                                 desc_advance(b0, (k >> 2) * L::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
                     }
-                    umma_commit(&ms.s_full[sb]);
+                    umma_commit_elect(&ms.s_full[sb]);
                     // last tile of this (CTA, sequence) pair: its Q buffer is free once these MMAs have run
-                    if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit(&ms.q_empty[wq.pair & 1]);
-                }
-            }
-        } else if (warp == 5) {
-            // =========================== PV issue (one lane) ===========================
-            if (lane == 0) {
-                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
-                const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
-                const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, MMA_M * 16, SWIZZLE_NONE); // + buffer
-                Walker wv; wv.init(prefix, p.batch, t_begin);
-                for (int g = 0; g < n_total; ++g) {
-                    // O^T += V^T P^T over the tokens of tile g, four blocks of 128 dims, as soon as P(g) is published
-                    const bool first = wv.seek(p, prefix, t_begin + g);
+                    if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit_elect(&ms.q_empty[wq.pair & 1]);
+                };
+                // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
+                auto issue_pv = [&](int g, bool first) {
                     const int st = g % NS, pb = g & 1;
-                    mbar_wait(&ms.p_full[pb], g / 2, abort_flag);
-                    // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
-                    if (first && wv.pair > 0) mbar_wait(&ms.o_free, wv.pair - 1, abort_flag);
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
                     const uint64_t b0 = desc_advance(d_pv_b, pb * L::P_BUF_BYTES);
@@ -303,12 +333,48 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     for (int j = 0; j < 4; ++j) {
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
-                            umma_f8(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
+                            umma_f8_elect(tmem + L::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
                                     desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
                         }
                     }
-                    umma_commit(&ms.kv_empty[st]);
-                    umma_commit(&ms.p_empty[pb]);
+                    umma_commit_elect(&ms.kv_empty[st]);
+                    umma_commit_elect(&ms.p_empty[pb]);
+                };
+                // Event driven: PV(g) as soon as P(g) is published (it frees the tile for the gather), else
+                // QK of the next tile as soon as it has landed, its S buffer is free and its Q is in place.
+                int nq = 0, nv = 0;
+                bool q_first = wq.seek(p, prefix, t_begin), v_first = wv.seek(p, prefix, t_begin);
+                long long t_idle = clock64();
+                uint32_t spins = 0;
+                while (nv < n_total) {
+                    bool pv_ready = nv < nq && mbar_try_nb(&ms.p_full[nv & 1], (uint32_t)(nv / 2) & 1u);
+                    // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
+                    if (pv_ready && v_first && wv.pair > 0) pv_ready = mbar_try_nb(&ms.o_free, (uint32_t)(wv.pair - 1) & 1u);
+                    bool qk_ready = !pv_ready && nq < n_total &&
+                                    mbar_try_nb(&ms.kv_full[nq % NS], (uint32_t)(nq / NS) & 1u) &&
+                                    mbar_try_nb(&ms.s_empty[nq & 1], (uint32_t)(nq / 2 - 1) & 1u);
+                    if (qk_ready && q_first) qk_ready = mbar_try_nb(&ms.q_full[wq.pair & 1], (uint32_t)(wq.pair / 2) & 1u);
+                    // every lane takes the same decision: the elected-lane instructions below need a converged warp
+                    pv_ready = __all_sync(0xffffffffu, pv_ready);
+                    qk_ready = !pv_ready && __all_sync(0xffffffffu, qk_ready);
+                    if (!pv_ready && !qk_ready && (++spins & 63u) == 0u) {
+                        if (spins == 64u) t_idle = clock64();
+                        const bool give_up = *abort_flag || clock64() - t_idle > WAIT_LIMIT_CYCLES;
+                        if (__any_sync(0xffffffffu, give_up)) {
+                            *abort_flag = 1;        // give up waiting; issue the rest regardless so that every commit still arrives
+                            if (nq < n_total) qk_ready = true; else pv_ready = true;
+                        }
+                    }
+                    __syncwarp();
+                    if (pv_ready) {
+                        issue_pv(nv, v_first);
+                        ++nv; spins = 0;
+                        if (nv < n_total) v_first = wv.seek(p, prefix, t_begin + nv);
+                    } else if (qk_ready) {
+                        issue_qk(nq);
+                        ++nq; spins = 0;
+                        if (nq < n_total) q_first = wq.seek(p, prefix, t_begin + nq);
+                    }
                 }
             }
         } else {
@@ -342,11 +408,17 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 }
                 named_bar_sync(1, 128);
             };
-            for (int g = 0; g < n_total; ++g) {
+            // The loop starts with one dry pass (g = -1) over the per-tile code, re-centering path included, on an empty
+            // key set: it synchronises with nobody and publishes nothing.  The softmax warps are idle until the first
+            // scores exist (several microseconds); a first execution of this code costs one instruction-cache miss
+            // per 128 bytes of it, and when that happened on the first real tile - while every SM was filling its
+            // stages from HBM - the first softmax took 4 us instead of 0.7 us and held the whole pipeline back.
+            for (int g = -1; g < n_total; ++g) {
+                const bool dry = g < 0;
                 const int sb = g & 1;
-                const bool first = wk.seek(p, prefix, t_begin + g);
-                const bool last = t_begin + g + 1 == min(t_end, wk.seq_t1);
-                const int pos_first = (t_begin + g - wk.seq_t0) * TILE;
+                const bool first = dry ? true : wk.seek(p, prefix, t_begin + g);
+                const bool last = !dry && t_begin + g + 1 == min(t_end, wk.seq_t1);
+                const int pos_first = dry ? 0 : (t_begin + g - wk.seq_t0) * TILE;
                 if (first) {
 #pragma unroll
                     for (int c = 0; c < N; ++c) { nm[c] = INFINITY; l_acc[c] = 0.0f; }
@@ -355,18 +427,18 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     for (int q = 0; q < N / 16; ++q) {
                         const int j = (row0 + 16 * q) / p.heads;
                         const int causal_lim = p.causal ? (wk.tot_len - p.q_len + j + 1 - wk.pos_off) : 0x7fffffff;
-                        lim[q] = min(wk.seq_len, causal_lim);
+                        lim[q] = dry ? 0 : min(wk.seq_len, causal_lim);
                         lim_min = min(lim_min, lim[q]);
                     }
                 }
-                mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
+                if (!dry) mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
                 tc_fence_after();
                 float s[N];
 #pragma unroll
                 for (int c0 = 0; c0 < N; c0 += 16) tmem_ld16(tmem + lane_base + L::TMEM_S + sb * N + c0, s + c0);
                 tmem_wait_ld();
                 tc_fence_before();
-                mbar_arrive(&ms.s_empty[sb]);
+                if (!dry) mbar_arrive(&ms.s_empty[sb]);
 
                 // x = log2-domain exponent of the stored probability: score*scale - m_ref + P_SCALE_LOG2
                 const int pos = tid < TILE ? pos_first + tid : 0x7fffffff;           // lanes beyond the tile: always masked
@@ -381,7 +453,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 float xm = x[0];
 #pragma unroll
                 for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
-                const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
+                const bool recenter = named_bar_or(1, 128, dry || xm > P_SCALE_LOG2 + RECENTER);
                 if (recenter) {
                     float mx[N];
 #pragma unroll
@@ -444,7 +516,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (MMA_M * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
                 fence_proxy_async();
-                mbar_arrive(&ms.p_full[sb]);
+                if (!dry) mbar_arrive(&ms.p_full[sb]);
 
                 if (last) {
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out

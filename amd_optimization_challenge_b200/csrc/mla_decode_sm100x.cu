@@ -20,8 +20,7 @@
 //
 // Operand tile: four 128-byte-wide panels (dims 0..511, 128B swizzle; read K-major by QK and MN-major
 // by PV) and one 64-byte-wide panel (dims 512..575, 64B swizzle; QK only).
-// Roles: warps 0-3 softmax / epilogue, warp 4 QK issue, warp 5 PV issue (two issuing threads: one thread sustains one
-// tcgen05.mma per ~57 cycles at these shapes, the tensor pipe one per ~41), then PW gather warps (the whole tile for an e4m3 cache;
+// Roles: warps 0-3 softmax / epilogue, warp 4 MMA issue, then PW gather warps (the whole tile for an e4m3 cache;
 // only Q and the hybrid rope bytes next to transform warps), then XW transform warps.
 // Role in the reference: the MXFP4 split-KV stage-1 kernels (mixed-mla/submission.py:122-250,
 // mixed-mla/versions/hip_mxfp4_v5/submission.py:214-656) and their block decode
@@ -56,8 +55,7 @@ struct Cfg {
     static constexpr int PW = XF ? 1 : (N == 16 ? 8 : 4);
     static constexpr int XW = XF ? ((N == 16 || (ROPE_SEP && !QSPLIT)) ? 8 : 4) : 0;
     static constexpr int PRODUCERS = 32 * PW, XT = 32 * XW;
-    static constexpr int FIRST_PRODUCER = 192;                     // warps 0-3 softmax, 4 QK issue, 5 PV issue
-    static constexpr int THREADS = FIRST_PRODUCER + PRODUCERS + XT;
+    static constexpr int THREADS = 160 + PRODUCERS + XT;
     static constexpr int NB = KVFMT == KV_MXFP4 ? 18 : 16;        // 32-code blocks per cache row
     static constexpr int RAW_ROW = NB * 16;                       // bytes of codes per row
     static constexpr int PITCH = RAW_ROW + 16;                    // row pitch in a landing buffer: eight rows hit eight bank groups
@@ -188,9 +186,9 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
-        if (warp >= 6 && warp < 6 + C::PW) {
+        if (warp >= 5 && warp < 5 + C::PW) {
             // =========================== gather ===========================
-            const int pt = tid - C::FIRST_PRODUCER;
+            const int pt = tid - 160;
             Walker wk; wk.init(prefix, p.batch, t_begin);
             Walker wn = wk;                                       // one tile ahead, for the page-table prefetch
             constexpr int SLOTS_PER_THREAD = (TILE + PRODUCERS - 1) / PRODUCERS;
@@ -315,56 +313,51 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             }
             cp_async_wait_all();
         } else if (warp == 4) {
-            // =========================== QK issue (one lane) ===========================
-            // tcgen05.commit tracks the MMAs of the committing thread: s_full / q_empty follow this stream,
-            // kv_empty / kv_rows_free / p_empty the PV stream (QK of a tile is complete before its softmax, hence before its PV).
-            if (lane == 0) {
+            // =========================== MMA issue (whole warp, one elected lane per instruction) ===========================
+            {
                 constexpr uint32_t IDESC_QK = make_idesc(TILE, NQ, false, false);
+                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
                 // descriptor bases; per-MMA descriptors differ only in the start address
                 const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                              // + stage
                 const uint64_t d_qk_a_rope = make_desc(smem_base + 4 * PANEL_BYTES, 16, 512, SWIZZLE_64B);         // + stage
                 const uint64_t d_qk_b = make_desc(smem_base + C::OFF_Q, 16, 1024, SWIZZLE_128B);
                 const uint64_t d_qk_b_rope = make_desc(smem_base + C::OFF_Q + 4 * C::Q_PANEL_BYTES, 16, 512, SWIZZLE_64B);
-                Walker wq; wq.init(prefix, p.batch, t_begin);
-                for (int g = 0; g < n_total; ++g) {
-                    // S^T[128 tok x NQ] = K . Q^T for tile g; a hybrid cache keeps the rope dims in columns of their own
-                    const bool first = wq.seek(p, prefix, t_begin + g);
+                const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);                     // + stage
+                const uint64_t d_pv_b = make_desc(smem_base + C::OFF_P, 128, TILE * 16, SWIZZLE_NONE);             // + buffer
+                Walker wq, wv;                                    // the QK stream runs ahead of the PV stream
+                wq.init(prefix, p.batch, t_begin);
+                wv = wq;
+                // S^T[128 tok x NQ] = K . Q^T for tile g; a hybrid cache keeps the rope dims in columns of their own.
+                // QK_PARTS > 1 would issue it in pieces with PVs in between; measured slower (alternating the two MMA
+                // shapes costs more than the PV gains), so it stays in one piece.
+                constexpr int QK_PARTS = 1;
+                auto issue_qk = [&](int g, int part) {
                     const int st = g % NS, sb = g & 1;
-                    mbar_wait(&ms.kv_full[st], g / NS, abort_flag);
-                    mbar_wait(&ms.s_empty[sb], g / 2 - 1, abort_flag);
-                    if (first) mbar_wait(&ms.q_full, wq.pair, abort_flag);
-                    fence_proxy_async();   // cp.async wrote through the generic proxy; the MMA reads through the async proxy
-                    tc_fence_after();
+                    if (part == 0) {
+                        fence_proxy_async();   // cp.async wrote through the generic proxy; the MMA reads through the async proxy
+                        tc_fence_after();
+                    }
                     const uint32_t d_lat = tmem + sb * C::SC, d_rope = d_lat + (C::ROPE_SEP ? NQ : 0);
 #pragma unroll
-                    for (int k = 0; k < 18; ++k) {
+                    for (int kk = 0; kk < 18 / QK_PARTS; ++kk) {
+                        const int k = part * (18 / QK_PARTS) + kk;
                         if (k < 16) {
-                            umma_f8(d_lat, desc_advance(d_qk_a, st * STAGE_BYTES + (k >> 2) * PANEL_BYTES + (k & 3) * 32),
+                            umma_f8_elect(d_lat, desc_advance(d_qk_a, st * STAGE_BYTES + (k >> 2) * PANEL_BYTES + (k & 3) * 32),
                                     desc_advance(d_qk_b, (k >> 2) * C::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
                         } else {
-                            umma_f8(d_rope, desc_advance(d_qk_a_rope, st * STAGE_BYTES + (k - 16) * 32),
+                            umma_f8_elect(d_rope, desc_advance(d_qk_a_rope, st * STAGE_BYTES + (k - 16) * 32),
                                     desc_advance(d_qk_b_rope, (k - 16) * 32), IDESC_QK, (!C::ROPE_SEP || k > 16) ? 1u : 0u);
                         }
                     }
-                    umma_commit(&ms.s_full[sb]);
-                    // last tile of this (CTA, sequence) pair: the Q buffer is free once these MMAs have run
-                    if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit(&ms.q_empty);
-                }
-            }
-        } else if (warp == 5) {
-            // =========================== PV issue (one lane) ===========================
-            if (lane == 0) {
-                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
-                const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);                     // + stage
-                const uint64_t d_pv_b = make_desc(smem_base + C::OFF_P, 128, TILE * 16, SWIZZLE_NONE);             // + buffer
-                Walker wv; wv.init(prefix, p.batch, t_begin);
-                for (int g = 0; g < n_total; ++g) {
-                    // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims, as soon as P(g) is published
-                    const bool first = wv.seek(p, prefix, t_begin + g);
+                    if (part == QK_PARTS - 1) {
+                        umma_commit_elect(&ms.s_full[sb]);
+                        // last tile of this (CTA, sequence) pair: the Q buffer is free once these MMAs have run
+                        if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit_elect(&ms.q_empty);
+                    }
+                };
+                // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
+                auto issue_pv = [&](int g, bool first) {
                     const int st = g % NS, pb = g & 1;
-                    mbar_wait(&ms.p_full[pb], g / 2, abort_flag);
-                    // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
-                    if (first && wv.pair > 0) mbar_wait(&ms.o_free, wv.pair - 1, abort_flag);
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
                     const uint64_t b0 = desc_advance(d_pv_b, pb * C::P_BUF_BYTES);
@@ -374,16 +367,57 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            umma_f8(tmem + C::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
+                            umma_f8_elect(tmem + C::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
                                     desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
                         }
-                        if (C::ROWS_EARLY) umma_commit(&ms.kv_rows_free[st][kk]);
+                        if (C::ROWS_EARLY) umma_commit_elect(&ms.kv_rows_free[st][kk]);
                     }
-                    umma_commit(&ms.kv_empty[st]);
-                    umma_commit(&ms.p_empty[pb]);
+                    umma_commit_elect(&ms.kv_empty[st]);
+                    umma_commit_elect(&ms.p_empty[pb]);
+                };
+                // Event driven: PV(g) as soon as P(g) is published (it frees the tile for the next one), else
+                // QK of the next tile as soon as it is in place, its S buffer is free and its Q has landed.
+                int nq = 0, nv = 0, qk_part = 0;
+                bool q_first = wq.seek(p, prefix, t_begin), v_first = wv.seek(p, prefix, t_begin);
+                long long t_idle = clock64();
+                uint32_t spins = 0;
+                while (nv < n_total) {
+                    bool pv_ready = nv < nq && mbar_try_nb(&ms.p_full[nv & 1], (uint32_t)(nv / 2) & 1u);
+                    // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
+                    if (pv_ready && v_first && wv.pair > 0) pv_ready = mbar_try_nb(&ms.o_free, (uint32_t)(wv.pair - 1) & 1u);
+                    bool qk_ready = !pv_ready && nq < n_total &&
+                                    (qk_part > 0 ||
+                                     (mbar_try_nb(&ms.kv_full[nq % NS], (uint32_t)(nq / NS) & 1u) &&
+                                      mbar_try_nb(&ms.s_empty[nq & 1], (uint32_t)(nq / 2 - 1) & 1u) &&
+                                      (!q_first || mbar_try_nb(&ms.q_full, (uint32_t)wq.pair & 1u))));
+                    // every lane takes the same decision: the elected-lane instructions below need a converged warp
+                    pv_ready = __all_sync(0xffffffffu, pv_ready);
+                    qk_ready = !pv_ready && __all_sync(0xffffffffu, qk_ready);
+                    if (!pv_ready && !qk_ready && (++spins & 63u) == 0u) {
+                        if (spins == 64u) t_idle = clock64();
+                        const bool give_up = *abort_flag || clock64() - t_idle > WAIT_LIMIT_CYCLES;
+                        if (__any_sync(0xffffffffu, give_up)) {
+                            *abort_flag = 1;        // give up waiting; issue the rest regardless so that every commit still arrives
+                            if (nq < n_total) qk_ready = true; else pv_ready = true;
+                        }
+                    }
+                    __syncwarp();
+                    if (pv_ready) {
+                        issue_pv(nv, v_first);
+                        ++nv; spins = 0;
+                        if (nv < n_total) v_first = wv.seek(p, prefix, t_begin + nv);
+                    } else if (qk_ready) {
+                        issue_qk(nq, qk_part);
+                        spins = 0;
+                        if (++qk_part == QK_PARTS) {
+                            qk_part = 0;
+                            ++nq;
+                            if (nq < n_total) q_first = wq.seek(p, prefix, t_begin + nq);
+                        }
+                    }
                 }
             }
-        } else if (C::XF && warp >= 6 + C::PW) {
+        } else if (C::XF && warp >= 5 + C::PW) {
             // =========================== transform (block-scaled caches) ===========================
             // Warp xw owns the 16-token units xw, xw + XW, ... of every tile and S private landing buffers.  For each
             // unit it fetches the raw rows itself (16-byte cp.async of the codes, the aligned 8-byte words around the
@@ -396,7 +430,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             constexpr int UPW = (TILE / UNIT_TOK) / (C::XW > 0 ? C::XW : 1);   // units per warp per tile
             constexpr int S = C::S > 0 ? C::S : 1;
             constexpr int CODE_IT = UNIT_TOK * C::NB / 32, PER = CODE_IT + 2;   // copy instructions per lane per unit: codes, E8M0 words
-            const int xw = warp - 6 - C::PW;
+            const int xw = warp - 5 - C::PW;
             const int tok = lane & (UNIT_TOK - 1), par = lane >> 4;
             const int J = n_total * UPW;                                  // units of this warp
             Walker wn; wn.init(prefix, p.batch, t_begin);

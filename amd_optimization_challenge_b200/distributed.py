@@ -44,6 +44,23 @@ def token_balanced_partition(kv_lens: Sequence[int], world: int) -> list[list[in
     return [sorted(s) for s in out]
 
 
+def split_kv_shard(kv_indices: torch.Tensor, batch: int, seq_len: int, rank: int, world: int, granule: int = 128):
+    """This rank's part of a uniform-length batch in the cross-GPU split-KV mode: the page-table
+    entries of keys [a, b) of every sequence, back to back, with the matching local kv_indptr,
+    position offsets and total lengths (int32, on kv_indices' device).  `kv_indices` is the
+    global page-size-1 table [batch * seq_len]."""
+    a, b = kv_range_partition(seq_len, world, granule)[rank]
+    n = b - a
+    dev = kv_indices.device
+    local = kv_indices.view(batch, seq_len)[:, a:b].contiguous().view(-1)
+    if n == 0:
+        local = torch.zeros(1, dtype=torch.int32, device=dev)      # never read: every local sequence is empty
+    indptr = (torch.arange(batch + 1, dtype=torch.int32, device=dev) * n).contiguous()
+    off = torch.full((batch,), a, dtype=torch.int32, device=dev)
+    tot = torch.full((batch,), seq_len, dtype=torch.int32, device=dev)
+    return local, indptr, off, tot, n
+
+
 def kv_range_partition(seq_len: int, world: int, granule: int = 128) -> list[tuple[int, int]]:
     """Contiguous key ranges [begin, end) per rank for the cross-GPU split-KV mode, boundaries
     rounded to `granule` tokens (the kernels' tile) so that no tile straddles two GPUs."""
@@ -124,19 +141,29 @@ class SplitKVDecoder:
                 g[:, self.n_o:].unflatten(1, (self.rows, self.heads)))
 
     # one decode step ------------------------------------------------------------------------
-    def step(self, partial_fn: Callable, merge_fn: Callable | None = None):
+    def step(self, partial_fn: Callable, merge_fn: Callable | None = None, events=None):
         """partial_fn(out_o, out_lse) must fill this rank's normalised partial O and LSE (views
-        of the send buffer); returns the merged bf16 O [rows, heads, 512] on every rank."""
+        of the send buffer); returns the merged bf16 O [rows, heads, 512] on every rank.
+        `events`, if given, are three CUDA events recorded on the current stream before the
+        all-gather, after it and after the merge (for timing the three phases separately)."""
         partial_fn(self.local_o(), self.local_lse())
+        if events is not None:
+            events[0].record()
         if self.world > 1:
             dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
         else:
             self.recv.copy_(self.send)
-        o_parts, lse_parts = self.gathered()
+        if events is not None:
+            events[1].record()
         if merge_fn is None:
             from .submission import combine_partials_strided
-            return combine_partials_strided(self.recv, self.world, self.n, self.n_o, self.rows, self.heads)
-        return merge_fn(o_parts, lse_parts)
+            out = combine_partials_strided(self.recv, self.world, self.n, self.n_o, self.rows, self.heads)
+        else:
+            o_parts, lse_parts = self.gathered()
+            out = merge_fn(o_parts, lse_parts)
+        if events is not None:
+            events[2].record()
+        return out
 
 
 def cuda_partial_fn(q, q_scale, kv_format: str, kv_local, kv_indptr_local, *, sm_scale: float, q_len: int,

@@ -25,6 +25,7 @@ from __future__ import annotations
 import argparse
 import ctypes
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -152,18 +153,210 @@ def time_cpu(host, reps):
     return statistics.median(ts)
 
 
+# ---------------------------------------------------------------------------------------------------
+# the two sharded multi-GPU modes, measured inside the default run when it spans more than one GPU
+# ---------------------------------------------------------------------------------------------------
+
+def _gpu_time_us(fn, steps, dev, dist=None, world=1, spin_cycles=int(4e7)):
+    """Device time per step of `fn`, microseconds, max over ranks.  The steps are queued behind a GPU spin so
+    that the host's launch work for all of them is done before the first one runs (the same number of
+    steps on every rank, so that collectives inside `fn` pair up)."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None and world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(spin_cycles)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / steps], device=dev)
+    if dist is not None and world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _stage1_us(pkg, fn, reps, dev, dist=None, world=1):
+    """Mean duration of the stage-1 launch inside `fn` (events recorded by the library), max over ranks."""
+    lib = pkg._cabi.lib
+    pairs = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); b.record()
+        pairs.append((a, b))
+    torch.cuda.synchronize()
+    torch.cuda._sleep(int(2e7))
+    for a, b in pairs:
+        lib.b200_mla_set_stage1_events(ctypes.c_void_p(a.cuda_event), ctypes.c_void_p(b.cuda_event))
+        fn()
+    lib.b200_mla_set_stage1_events(None, None)
+    torch.cuda.synchronize()
+    t = torch.tensor([statistics.mean(a.elapsed_time(b) for a, b in pairs) * 1e3], device=dev)
+    if dist is not None and world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sharded_modes(pkg, dist, rank, world, dev, kernel="auto", steps=30):
+    """BASELINE configs 3 and 4 in the multi-GPU modes they are defined for, on `world` GPUs, next to the same
+    workload on ONE GPU measured in the same process group (every rank runs the whole problem on its own GPU
+    with no collective; max over ranks).  Inputs are drawn on the GPU from one seed, so every rank holds the
+    identical global problem and takes its shard of it."""
+    import amd_optimization_challenge_b200.inputs as gen
+    from amd_optimization_challenge_b200.distributed import (SplitKVDecoder, cuda_partial_fn, shard_batch,
+                                                             split_kv_shard, token_balanced_partition)
+    out = {}
+
+    # ---- config 3: token-balanced batch sharding, no data-path collective
+    w = WORKLOADS["c3"]
+    lens = make_lens(w, 1234)
+    full = gen.generate_input(w["batch"], 1, max(lens), 1234, num_heads=w["heads"], kv_lens=lens, shuffle_pages=True,
+                              formats=("hybrid",), device=dev, generator_device="cuda")
+    cfg = dict(full[4], kv_format="hybrid", q_format="fp8", impl=kernel)
+    full = (full[0], full[1], full[2], full[3], cfg)
+    ids = token_balanced_partition(lens, world)[rank]
+    mine = shard_batch(full, ids)
+    t1 = _gpu_time_us(lambda: pkg.custom_kernel(full), steps, dev, dist, world)
+    tn = _gpu_time_us(lambda: pkg.custom_kernel(mine), steps, dev, dist, world)
+    s1 = _stage1_us(pkg, lambda: pkg.custom_kernel(mine), 10, dev, dist, world)
+    tokens = w["batch"] * w["q_len"]
+    loads = [sum(lens[i] for i in part) for part in token_balanced_partition(lens, world)]
+    out["c3"] = {"mode": "token-balanced batch shard, no collective", "us_per_step": tn, "tokens_per_s": tokens / (tn * 1e-6),
+                 "stage1_us_max_rank": s1, "n1_us_per_step": t1, "speedup_vs_n1": t1 / tn,
+                 "efficiency_vs_n1": t1 / tn / world, "kv_tokens_per_rank": {"min": min(loads), "max": max(loads)},
+                 "limiter": "stage-1 kernel of the most loaded rank (no exchange step)"}
+    del full, mine
+    torch.cuda.empty_cache()
+
+    # ---- config 4: each sequence's keys split over the GPUs, one all-gather of (O || LSE), LSE merge
+    w = WORKLOADS["c4"]
+    B, QL, S = w["batch"], w["q_len"], w["kv_len"]
+    full = gen.generate_input(B, QL, S, 4321, num_heads=w["heads"], shuffle_pages=True, formats=("mxfp4",),
+                              device=dev, generator_device="cuda")
+    q, kvd, _, _, cfg = full
+    cfg1 = dict(cfg, kv_format="mxfp4", q_format="bf16", impl=kernel)
+    t1 = _gpu_time_us(lambda: pkg.custom_kernel((q, kvd, full[2], full[3], cfg1)), steps, dev, dist, world)
+    idx, ip, off, tot, n_loc = split_kv_shard(cfg["kv_indices"], B, S, rank, world)
+    dec = SplitKVDecoder(B * QL, w["heads"], dev)
+    part = cuda_partial_fn(q, None, "mxfp4", kvd["mxfp4"], ip, sm_scale=cfg["sm_scale"], q_len=QL, kv_indices=idx,
+                           kv_pos_offset=off, kv_total_len=tot, total_kv_hint=max(B * n_loc, 1), impl=kernel)
+    tn = _gpu_time_us(lambda: dec.step(part), steps, dev, dist, world)
+    s1 = _stage1_us(pkg, lambda: dec.step(part), 10, dev, dist, world)
+    # the three phases of a step, timed apart on the device
+    trip = [tuple(torch.cuda.Event(enable_timing=True) for _ in range(3)) for _ in range(10)]
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda._sleep(int(2e7))
+    for ev in trip:
+        dec.step(part, events=ev)
+    torch.cuda.synchronize()
+    ph = torch.tensor([statistics.mean(e[0].elapsed_time(e[1]) for e in trip) * 1e3,
+                       statistics.mean(e[1].elapsed_time(e[2]) for e in trip) * 1e3], device=dev)
+    dist.all_reduce(ph, op=dist.ReduceOp.MAX)
+    ag_us, merge_us = float(ph[0]), float(ph[1])
+    tokens = B * QL
+    gathered = world * dec.n * 4
+    out["c4"] = {"mode": "cross-GPU split-KV, one NCCL all-gather of (O || LSE), LSE merge", "us_per_step": tn,
+                 "tokens_per_s": tokens / (tn * 1e-6), "stage1_us_max_rank": s1, "all_gather_us": ag_us,
+                 "merge_us": merge_us, "all_gather_bytes_received": gathered, "n1_us_per_step": t1,
+                 "speedup_vs_n1": t1 / tn, "efficiency_vs_n1": t1 / tn / world,
+                 "limiter": "stage-1 kernel" if s1 > 2 * (ag_us + merge_us) else "all-gather + merge",
+                 "launch": "eager, queued behind a GPU spin; the all-gather is NCCL on the decode stream's order"}
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# the reference's own benchmark shapes (task.yml:81-93): contiguous pages, all three caches in the tuple
+# ---------------------------------------------------------------------------------------------------
+
+REF8 = [(4, 1024, 4217), (4, 8192, 4220), (32, 1024, 5412), (32, 8192, 5415),
+        (64, 1024, 1357), (64, 8192, 1360), (256, 1024, 9823), (256, 8192, 9826)]
+
+
+def ref8_sweep(pkg, dev, reps=30):
+    """custom_kernel on the reference's untouched tuple for its eight benchmark shapes, FP8 route (the
+    reference's ref_kernel choice) and MXFP4 route: harness-style (synchronise, flush L2, events around ONE
+    eager call: eval.py:225-261) and as a CUDA-graph replay over rotated cache copies."""
+    import amd_optimization_challenge_b200.inputs as gen
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    for batch, kv_len, seed in REF8:
+        data = gen.generate_input(batch, 1, kv_len, seed, device=dev, generator_device="cuda")
+        q, kvd, qo, kvp, cfg = data
+        cfg.pop("total_kv", None)
+        row = {"batch": batch, "kv_len": kv_len}
+        for fmt in ("fp8", "mxfp4"):
+            c = dict(cfg) if fmt == "fp8" else dict(cfg, kv_format="mxfp4")
+            tup = (q, kvd, qo, kvp, c)
+            for _ in range(3):
+                pkg.custom_kernel(tup)
+            ts = []
+            for _ in range(reps):
+                torch.cuda.synchronize()
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                pkg.custom_kernel(tup)
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e3)
+            row[f"{fmt}_eager_us"] = statistics.mean(ts)
+            # graph replay over enough distinct copies of the cache to exceed L2
+            kv_bytes = sum(t.numel() * t.element_size() for t in kvd[fmt])
+            n_rot = min(6, max(2, -(-int(2.4 * L2_BYTES) // kv_bytes)))
+            rot = [tup] + [(q, dict(kvd, **{fmt: tuple(t.clone() for t in kvd[fmt])}), qo, kvp, c) for _ in range(n_rot - 1)]
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for r in rot:
+                        pkg.custom_kernel(r)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            for _ in range(3):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            row[f"{fmt}_graph_us"] = e0.elapsed_time(e1) * 1e3 / (10 * n_rot)
+            del graph, rot
+        rows.append(row)
+        del data, q, kvd
+        torch.cuda.empty_cache()
+    geo = lambda k: math.exp(sum(math.log(r[k]) for r in rows) / len(rows))
+    return {"shapes": rows, "geomean_us": {k: geo(k) for k in ("fp8_eager_us", "fp8_graph_us", "mxfp4_eager_us", "mxfp4_graph_us")},
+            "note": "contiguous pages (no kv_indices), tuple and config exactly as reference.generate_input builds them; "
+                    "eager = synchronise, flush L2, CUDA events around one call (the reference harness's timing); B200"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["ref8"])
+    ap.add_argument("--no-sharded", action="store_true", help="with N > 1: skip the sharded c3 / c4 measurements")
     ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tcgen05"])
     ap.add_argument("--cpu-reps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager API calls instead of a CUDA graph replay")
     args = ap.parse_args()
+    if args.workload == "ref8":
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        import amd_optimization_challenge_b200 as pkg
+        print(json.dumps({"metric": "mla_decode_us_per_call", "unit": "us", "higher_is_better": False, "n_gpus": 1,
+                          "data": "synthetic", "config": {"workload": "ref8: the reference's eight benchmark shapes (task.yml:81-93)"},
+                          "ref8": ref8_sweep(pkg, torch.device("cuda", torch.cuda.current_device()))}), flush=True)
+        return
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -378,28 +571,52 @@ def main():
     pin = lambda t: t.contiguous().pin_memory()
     h_q, h_kv = pin(host["q"]), tuple(pin(t) for t in host["kv"])
     h_idx, h_ip, h_qo = pin(host["kv_indices"]), pin(host["kv_indptr"]), pin(host["qo"])
-    d_q, d_kv = torch.empty_like(base[0]), tuple(torch.empty_like(t) for t in base[1][w["kv_format"]])
-    d_idx, d_ip, d_qo = torch.empty_like(base[4]["kv_indices"]), torch.empty_like(base[3]), torch.empty_like(base[2])
     h_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in (h_q, *h_kv, h_idx, h_ip, h_qo))
     d2h = h_out.numel() * h_out.element_size()
-    cfg_e = dict(base[4]); cfg_e["kv_indices"] = d_idx
 
-    def e2e_step():
-        d_q.copy_(h_q, non_blocking=True)
-        for d, h in zip(d_kv, h_kv):
-            d.copy_(h, non_blocking=True)
-        d_idx.copy_(h_idx, non_blocking=True); d_ip.copy_(h_ip, non_blocking=True); d_qo.copy_(h_qo, non_blocking=True)
-        o = call((d_q, {w["kv_format"]: d_kv}, d_qo, d_ip, cfg_e))
-        h_out.copy_(o, non_blocking=True)
+    # Two device-side input sets: the copies of step i + 1 run on a copy stream while the kernels of step i run on the
+    # compute stream (every step still uploads all of its inputs and reads its output back inside the timed region).
+    def dev_set():
+        cfg_e = dict(base[4])
+        cfg_e["kv_indices"] = torch.empty_like(base[4]["kv_indices"])
+        return dict(q=torch.empty_like(base[0]), kv=tuple(torch.empty_like(t) for t in base[1][w["kv_format"]]),
+                    ip=torch.empty_like(base[3]), qo=torch.empty_like(base[2]), cfg=cfg_e,
+                    ready=torch.cuda.Event(), free=torch.cuda.Event())
+    sets = [dev_set(), dev_set()]
+    copy_stream = torch.cuda.Stream()
+
+    def stage(s):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(s["free"])                   # the kernels that read this set last have finished
+            s["q"].copy_(h_q, non_blocking=True)
+            for d, h in zip(s["kv"], h_kv):
+                d.copy_(h, non_blocking=True)
+            s["cfg"]["kv_indices"].copy_(h_idx, non_blocking=True)
+            s["ip"].copy_(h_ip, non_blocking=True); s["qo"].copy_(h_qo, non_blocking=True)
+            s["ready"].record(copy_stream)
+
+    def e2e_run(n, start_event=None):
+        cur = torch.cuda.current_stream()
+        if start_event is not None:
+            copy_stream.wait_event(start_event)                 # the first upload starts inside the timed region
+        stage(sets[0])
+        for k in range(n):
+            s = sets[k & 1]
+            if k + 1 < n:
+                stage(sets[(k + 1) & 1])
+            cur.wait_event(s["ready"])
+            o = call((s["q"], {w["kv_format"]: s["kv"]}, s["qo"], s["ip"], s["cfg"]))
+            h_out.copy_(o, non_blocking=True)
+            s["free"].record(cur)
 
     e_steps = max(3, min(args.steps, 20))
-    for _ in range(3):
-        e2e_step()
+    for st_ in sets:
+        st_["free"].record(torch.cuda.current_stream())
+    e2e_run(3)
     barrier()
     ev0.record()
-    for _ in range(e_steps):
-        e2e_step()
+    e2e_run(e_steps, ev0)
     ev1.record()
     barrier()
     e_ms = ev0.elapsed_time(ev1) / e_steps
@@ -408,7 +625,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e_ms = float(t.item())
     e2e = {"value": tokens_job / (e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "note": "inputs staged from pinned host memory into two device-side sets; the upload of step i+1 overlaps the kernels of step i"}
 
     # ---- CPU baseline (rank 0, single-GPU runs only)
     cpu = None
@@ -431,6 +649,9 @@ def main():
     per_gpu = {"replica": "each rank decodes its own batch, no collective",
                "batch_shard": "token-balanced split of the batch over the ranks, no collective",
                "split_kv": "each sequence's keys split over the ranks; (O || LSE) partials exchanged by one NCCL all-gather, then the LSE merge"}[mode]
+    sharded = None
+    if world > 1 and args.workload == "c1" and not args.no_sharded:
+        sharded = sharded_modes(pkg, dist, rank, world, dev, args.kernel)
     if rank == 0:
         line = {
             "metric": "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n_gpus,
@@ -448,6 +669,8 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
             "gpu_launches": launches_per_step * args.steps,
         }
+        if sharded is not None:
+            line["sharded"] = sharded
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -58,8 +58,6 @@ def test_official_test_shapes_untouched_tuple(pkg, batch, q_len, kv_len, seed):
     torch.cuda.synchronize()
     for b, o in _sampled_oracle(data, "mxfp4", "bf16", seqs[:2]).items():
         assert_close(out4[b * q_len:(b + 1) * q_len], o, tight=1.5e-2)
-    # the two caches hold the same keys: their outputs agree to quantisation noise
-    assert_close(out4, out, rtol=5e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("impl", ["generic", "tcgen05"])
