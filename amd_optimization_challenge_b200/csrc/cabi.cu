@@ -133,6 +133,7 @@ int32_t b200_mla_decode(const b200_mla_decode_args* a, void* stream_) {
     p.kv_bs = (const uint8_t*)a->kv_block_scales; p.kv_bs_stride = a->kv_block_scales_stride;
     p.kv_rope = (const uint8_t*)a->kv_rope; p.kv_rope_stride = a->kv_rope_stride;
     p.kv_scale = a->kv_scale; p.num_slots = a->num_slots; p.total_kv_hint = a->total_kv_hint > 0 ? a->total_kv_hint : 0;
+    p.last_slot = (unsigned int)((a->num_slots < 0x80000000LL ? a->num_slots : 0x80000000LL) - 1);
     p.kv_indptr = a->kv_indptr; p.kv_indices = a->kv_indices; p.kv_page_indptr = a->kv_page_indptr;
     p.kv_pos_offset = a->kv_pos_offset; p.kv_total_len = a->kv_total_len;
     p.out = (__nv_bfloat16*)a->out; p.out_o_f32 = a->out_o_f32; p.out_lse = a->out_lse;

@@ -38,6 +38,7 @@ struct MlaParams {
     const uint8_t* kv_bs; long long kv_bs_stride;
     const uint8_t* kv_rope; long long kv_rope_stride;
     const float* kv_scale; long long num_slots;
+    unsigned int last_slot;             // min(num_slots, 2^31) - 1: the row an out-of-range page id is redirected to
     long long total_kv_hint;            // > 0: the host's bound on kv_indptr[batch]; kv_indices holds at least that many tokens' ids
     const int* kv_indptr; const int* kv_indices; const int* kv_page_indptr;
     const int* kv_pos_offset; const int* kv_total_len;
@@ -132,22 +133,45 @@ __device__ __forceinline__ int seq_of_tile(const int* prefix, int batch, int t) 
     return lo;
 }
 
-// Cache slot of the token at position `pos` of sequence b, or -1 when the page table points outside the
-// cache planes (slot < 0 or >= num_slots).  Such a row is never read: the callers treat it like a row past
-// the end of the sequence (zero fill), and the ST_BAD_PAGE bit of the status word tells the host about it.
+// Cache slot of the token at position `pos` of sequence b, as the page table gives it (unchecked).
 __device__ __forceinline__ long long slot_of(const MlaParams& p, int b, int seq_base, int page_base, int pos) {
-    long long s;
-    if (p.kv_indices == nullptr) s = (long long)seq_base + pos;
-    else if (p.page_size == 1) s = (long long)p.kv_indices[page_base + pos];
-    else {
-        const int pg = pos / p.page_size;
-        s = (long long)p.kv_indices[page_base + pg] * p.page_size + (pos - pg * p.page_size);
+    if (p.kv_indices == nullptr) return (long long)seq_base + pos;
+    if (p.page_size == 1) return (long long)p.kv_indices[page_base + pos];
+    int pg = pos / p.page_size;
+    return (long long)p.kv_indices[page_base + pg] * p.page_size + (pos - pg * p.page_size);
+}
+// Row of the cache planes that is actually read for slot `s`: s itself inside [0, num_slots), else a row inside
+// (negative values, the "no row" marker -1 included, map to the last row).  Nothing outside the planes is ever read;
+// a key whose id needed the clamp reads as some other row, which check_span_pages reports as ST_BAD_PAGE.  The
+// clamp is applied where a slot is turned into an address, not where it is loaded: the kernels load page ids one or
+// two steps ahead of their use, and touching the value early would wait for that load (measured: 10-25 % of a call).
+__device__ __forceinline__ unsigned int clamp_slot(const MlaParams& p, int s) { return min((unsigned int)s, p.last_slot); }
+
+// Page ids of the tiles [t_begin, t_end) a stage-1 CTA owns: sets ST_BAD_PAGE if one of them names a page outside
+// the cache planes (or, without a page table, if a token range reaches beyond them).  Called by `nthreads` threads
+// (tid = 0 .. nthreads - 1) that have nothing else to do at the time; `tile` = tokens per tile.
+static __device__ __noinline__ void check_span_pages(const MlaParams& p, const int* prefix, int t_begin, int t_end, int tile,
+                                              int tid, int nthreads) {
+    bool bad = false;
+    int b = seq_of_tile(prefix, p.batch, t_begin);
+    for (int t = t_begin; t < t_end;) {
+        while (prefix[b + 1] <= t) ++b;
+        const int t1 = min(t_end, prefix[b + 1]);
+        const int seq_base = p.kv_indptr[b], len = max(p.kv_indptr[b + 1] - seq_base, 0);
+        const int pos0 = (t - prefix[b]) * tile, pos1 = min((t1 - prefix[b]) * tile, len);
+        if (p.kv_indices != nullptr) {
+            const int page_base = p.kv_page_indptr ? p.kv_page_indptr[b] : seq_base;
+            const int e0 = pos0 / p.page_size, e1 = (pos1 + p.page_size - 1) / p.page_size;
+            for (int e = e0 + tid; e < e1; e += nthreads) {
+                const long long id = p.kv_indices[page_base + e];
+                bad |= id < 0 || id * p.page_size >= p.num_slots;
+            }
+        } else if (tid == 0) {
+            bad |= seq_base < 0 || (long long)seq_base + pos1 > p.num_slots;
+        }
+        t = t1;
     }
-    if (s < 0 || s >= p.num_slots) {
-        atomicOr(p.status, (int)ST_BAD_PAGE);
-        return -1;
-    }
-    return s;
+    if (bad) atomicOr(p.status, (int)ST_BAD_PAGE);
 }
 
 // Position of one role inside the CTA's span of global tiles [t_begin, t_end): which sequence the

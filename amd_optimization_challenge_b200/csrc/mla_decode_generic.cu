@@ -62,8 +62,7 @@ __device__ __forceinline__ void load_tile(const MlaParams& p, int b, int seq_bas
         r.v[i] = make_uint4(0, 0, 0, 0);
         r.sc[i] = 127;
         if (tok < TILE && pos < pos_end) {
-            const long long slot = slot_of(p, b, seq_base, page_base, pos);
-            if (slot < 0) continue;                    // page id outside the cache: the row reads as zeros
+            const long long slot = clamp_slot(p, (int)slot_of(p, b, seq_base, page_base, pos));
             if (KVFMT == KV_E4M3) {
                 r.v[i] = __ldg(reinterpret_cast<const uint4*>(p.kv_codes + slot * p.kv_codes_stride) + c);
             } else if (KVFMT == KV_MXFP4) {
@@ -149,6 +148,7 @@ __global__ void __launch_bounds__(THREADS, 2) mla_decode_generic_kernel(const Ml
     if (TT == 0) return;
     const int t_begin = span_begin(prefix, p.batch, w, G), t_end = span_begin(prefix, p.batch, w + 1, G);
     if (t_begin >= t_end) return;
+    if (blockIdx.y == 0) check_span_pages(p, prefix, t_begin, t_end, TILE, tid, THREADS);
 
     // scalar scales: scores get q_scale * kv_scale(e4m3 cache) * sm_scale * log2e, outputs kv_scale
     const float q_sc = p.q_format == Q_E4M3 ? block_q_scale(block_q_amax_begin(p.q_amax_parts, p.q_cast), p.q_scale, p.q_cast, &s.q_amax) : 1.0f;

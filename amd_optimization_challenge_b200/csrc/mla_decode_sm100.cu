@@ -17,7 +17,8 @@
 //
 // Roles:  warps 0-3  softmax / correction / epilogue (one TMEM lane = one token / one output dim per thread)
 //         warp  4    tcgen05.mma issue (one lane, event driven), TMEM allocation
-//         warps 5..  paged gather: 16-byte cp.async of cache rows (and of Q) through the page table
+//         warps 5-6  Q rows of each sequence (copy, or load + per-tensor e4m3 quantisation of a bf16 Q)
+//         warps 7..  paged gather: 16-byte cp.async of cache rows through the page table
 //                    straight into the 128B-swizzled UMMA layout, completion signalled on an mbarrier.
 // Movers measured on B200 for shuffled 576-byte rows, device-wide, one CTA per SM:
 //         16-byte cp.async (LSU)                       3.5 - 4.4 TB/s, lands directly in operand layout
@@ -58,9 +59,11 @@ struct Layout {
     static constexpr int ROPE_PANEL_BYTES = TILE * 64;           // dims 512..575: 64-byte rows, 64B swizzle
     static constexpr int STAGE_BYTES = 4 * PANEL_BYTES + ROPE_PANEL_BYTES;
     static constexpr int NPANEL = 5;                             // Q keeps five 128-byte-wide panels
-    static constexpr int PRODUCER_WARPS = (N == 16) ? 9 : 2;     // N = 16: 288 = 8 x 36 threads, one 16-byte column and one row phase each; N = 32 needs the registers
+        static constexpr int PRODUCER_WARPS = (N == 16) ? 9 : 2;     // N = 16: 288 = 8 x 36 threads, one 16-byte column and one row phase each; N = 32 needs the registers
     static constexpr int PRODUCERS = 32 * PRODUCER_WARPS;
-    static constexpr int THREADS = 160 + PRODUCERS;
+    static constexpr int Q_THREADS = 64;                          // two warps load (and cast) the Q rows of each sequence
+    static constexpr int FIRST_PRODUCER = 160 + Q_THREADS;
+    static constexpr int THREADS = FIRST_PRODUCER + PRODUCERS;
     static constexpr int Q_PANEL_BYTES = N * 128;
     static constexpr int Q_BYTES = NPANEL * Q_PANEL_BYTES;        // one Q buffer (two of them: next sequence's Q loads early)
     static constexpr int P_CHUNKS = 2 * N / 16;                  // 16-column chunks of [hi | lo]
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128);
             mbar_init(&ms.p_full[i], 128); mbar_init(&ms.p_empty[i], 1);
-            mbar_init(&ms.q_full[i], PRODUCERS); mbar_init(&ms.q_empty[i], 1);
+            mbar_init(&ms.q_full[i], L::Q_THREADS); mbar_init(&ms.q_empty[i], 1);
         }
         for (int i = 0; i < SLOT_RING; ++i) mbar_init(&ms.slot_full[i], PRODUCERS);
         mbar_init(&ms.o_free, 128);
@@ -135,11 +138,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
-        if (warp >= 5) {
+        if (warp >= 7) {
             // =========================== gather ===========================
             // One stage = TILE tokens x 36 sixteen-byte columns.  Consecutive threads take consecutive
             // columns, so a warp instruction reads 512 contiguous bytes of (at most two) rows.
-            const int pt = tid - 160;
+            const int pt = tid - L::FIRST_PRODUCER;
             Walker wk; wk.init(prefix, p.batch, t_begin);
             Walker wn = wk;                                       // NS tiles ahead, for the page-table prefetch
             const bool paged = p.kv_indices != nullptr;
@@ -161,43 +164,19 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 }
                 cp_async_mbar_arrive_noinc(&ms.slot_full[g % SLOT_RING]);
             };
-            // cache slot of token `tok` of tile g (wk describes its sequence), -1 past the end of the sequence or when
-            // the page table points outside the cache planes (reported through the status word, the row reads as zeros)
+            // cache slot of token `tok` of tile g (wk describes its sequence), -1 past the end of the sequence
             auto slot_at = [&](int g, int pos0, int tok) -> int {
                 const int pos = pos0 + tok;
                 if (pos >= wk.seq_len) return -1;
-                long long sl;
-                if (!paged) sl = (long long)wk.seq_base + pos;
-                else {
-                    const int id = ms.slot[g % SLOT_RING][tok];
-                    sl = p.page_size == 1 ? (long long)id : (long long)id * p.page_size + (pos % p.page_size);
-                }
-                if (sl < 0 || sl >= p.num_slots) { atomicOr(p.status, (int)ST_BAD_PAGE); return -1; }
-                return (int)sl;
+                if (!paged) return wk.seq_base + pos;
+                const int id = ms.slot[g % SLOT_RING][tok];
+                return p.page_size == 1 ? id : id * p.page_size + (pos % p.page_size);
             };
 #pragma unroll 1
             for (int g = 0; g < NS; ++g) prefetch_ids(g);
             for (int g = 0; g < n_total; ++g) {
                 const int st = g % NS;
-                const bool first = wk.seek(p, prefix, t_begin + g);
-                // Q rows of a new sequence.  A bf16 Q that is cast on load is fetched into registers now (when a thread's share
-                // is small) so that its latency runs beside the tile's copies; it is converted and stored after they are issued.
-                constexpr int QV = (N * 72 + PRODUCERS - 1) / PRODUCERS;     // 16-byte bf16 vectors per thread
-                constexpr bool Q_PRELOAD = QV <= 8;
-                uint4 qv[Q_PRELOAD ? QV : 1];
-                auto q_src = [&](int i) {
-                    const int r = i / 72, v8 = i - r * 72;
-                    const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                    return reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
-                                                          (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8);
-                };
-                if (first && p.q_cast && Q_PRELOAD) {
-#pragma unroll
-                    for (int k = 0; k < QV; ++k) {
-                        const int i = pt + k * PRODUCERS;
-                        qv[Q_PRELOAD ? k : 0] = i < N * 72 ? __ldg(q_src(i)) : make_uint4(0u, 0u, 0u, 0u);
-                    }
-                }
+                wk.seek(p, prefix, t_begin + g);
                 const int pos0 = (t_begin + g - wk.seq_t0) * TILE;
                 if (paged) mbar_wait(&ms.slot_full[g % SLOT_RING], g / SLOT_RING, abort_flag);
                 mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
@@ -220,7 +199,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     prefetch_ids(g + NS);
 #pragma unroll
                     for (int i = 0; i < PER; ++i)
-                        cp_async16(dst0 + i * dstep, src0 + (long long)max(sl[i], 0) * p.kv_codes_stride, sl[i] < 0 ? 0u : 16u);
+                        cp_async16(dst0 + i * dstep, src0 + (long long)clamp_slot(p, sl[i]) * p.kv_codes_stride, sl[i] < 0 ? 0u : 16u);
                 } else {
                     constexpr int PER_TILE = (TILE * 36 + PRODUCERS - 1) / PRODUCERS;
                     constexpr int BATCH = PER_TILE < 16 ? PER_TILE : 16;
@@ -236,7 +215,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                             const int id = id0 + u * PRODUCERS;
                             if (sl[u] != -2) {
                                 const int tok = id / 36, c = id - tok * 36;
-                                const uint8_t* src = p.kv_codes + (long long)(sl[u] < 0 ? 0 : sl[u]) * p.kv_codes_stride + c * 16;
+                                const uint8_t* src = p.kv_codes + (long long)clamp_slot(p, sl[u]) * p.kv_codes_stride + c * 16;
                                 const uint32_t dst = c < 32 ? stage_addr + (c >> 3) * PANEL_BYTES + tok * 128 + (((c & 7) ^ (tok & 7)) << 4)
                                                             : stage_addr + 4 * PANEL_BYTES + tok * 64 + (((c - 32) ^ ((tok >> 1) & 3)) << 4);
                                 cp_async16(dst, src, sl[u] < 0 ? 0u : 16u);     // rows past the end of the sequence: zero fill
@@ -246,48 +225,58 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     prefetch_ids(g + NS);
                 }
                 cp_async_mbar_arrive_noinc(&ms.kv_full[st]);   // asynchronous: the thread does not wait for its copies
-                if (first) {
-                    // Q rows of the new sequence -> swizzled K-major panels of Q buffer (pair & 1)
-                    const int qb = wk.pair & 1;
-                    mbar_wait(&ms.q_empty[qb], wk.pair / 2 - 1, abort_flag);
-                    const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
-                    if (p.q_cast) {
-                        // bf16 rows, quantised here: eight values in, eight e4m3 bytes (half a 16-byte column) out
-                        unsigned char* q_smem = smem + L::OFF_Q + qb * L::Q_BYTES;
-                        auto put = [&](int i, const uint4& raw) {
-                            const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
-                            *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) =
-                                q_cast_e4m3x8(raw, q_sc);
-                        };
-                        if (Q_PRELOAD) {
+            }
+            cp_async_wait_all();
+        } else if (warp >= 5) {
+            // =========================== Q rows (two warps) ===========================
+            // One pass per (CTA, sequence) pair, one pair ahead of the QK stream (two Q buffers): the rows of the sequence
+            // -> swizzled K-major panels.  e4m3 rows are copied; bf16 rows that are quantised here (per-tensor, the
+            // reference's rule) are loaded, converted and stored.  Kept off the gather warps: the conversion of one
+            // sequence's rows takes several microseconds, during which they would not request cache rows.
+            const int pt = tid - 160;
+            constexpr int QT = L::Q_THREADS;
+            Walker wk; wk.init(prefix, p.batch, t_begin);
+            for (int t = t_begin; t < t_end; t = wk.seq_t1) {
+                wk.seek(p, prefix, t);
+                const int qb = wk.pair & 1;
+                mbar_wait(&ms.q_empty[qb], wk.pair / 2 - 1, abort_flag);
+                const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
+                if (p.q_cast) {
+                    // eight bf16 values in, eight e4m3 bytes (half a 16-byte column) out; eight loads in flight per thread
+                    unsigned char* q_smem = smem + L::OFF_Q + qb * L::Q_BYTES;
+                    auto q_src = [&](int i) {
+                        const int r = i / 72, v8 = i - r * 72;
+                        const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                        return reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                                                              (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8);
+                    };
+#pragma unroll 1
+                    for (int i0 = pt; i0 < N * 72; i0 += 8 * QT) {
+                        uint4 raw[8];
 #pragma unroll
-                            for (int k = 0; k < QV; ++k) {
-                                const int i = pt + k * PRODUCERS;
-                                if (i < N * 72) put(i, qv[Q_PRELOAD ? k : 0]);
-                            }
-                        } else {
-                            for (int i0 = pt; i0 < N * 72; i0 += 8 * PRODUCERS) {     // eight loads in flight, then their conversion
-                                uint4 raw[8];
+                        for (int u = 0; u < 8; ++u)
+                            if (i0 + u * QT < N * 72) raw[u] = __ldg(q_src(i0 + u * QT));
 #pragma unroll
-                                for (int u = 0; u < 8; ++u)
-                                    if (i0 + u * PRODUCERS < N * 72) raw[u] = __ldg(q_src(i0 + u * PRODUCERS));
-#pragma unroll
-                                for (int u = 0; u < 8; ++u)
-                                    if (i0 + u * PRODUCERS < N * 72) put(i0 + u * PRODUCERS, raw[u]);
+                        for (int u = 0; u < 8; ++u) {
+                            const int i = i0 + u * QT;
+                            if (i < N * 72) {
+                                const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
+                                *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) =
+                                    q_cast_e4m3x8(raw[u], q_sc);
                             }
                         }
-                        fence_proxy_async();                      // the MMA reads Q through the async proxy
-                        mbar_arrive(&ms.q_full[qb]);
-                    } else {
-                        for (int i = pt; i < N * 36; i += PRODUCERS) {
-                            const int r = i / 36, c = i - r * 36;
-                            const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
-                                                 (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
-                            cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
-                        }
-                        cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
                     }
+                    fence_proxy_async();                      // the MMA reads Q through the async proxy
+                    mbar_arrive(&ms.q_full[qb]);
+                } else {
+                    for (int i = pt; i < N * 36; i += QT) {
+                        const int r = i / 36, c = i - r * 36;
+                        const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
+                                             (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
+                        cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
+                    }
+                    cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
                 }
             }
             cp_async_wait_all();
@@ -382,6 +371,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
             const float out_scale = kv_sc;
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+            // idle until the first scores exist: look over the page ids of this CTA's span (reporting only, see clamp_slot)
+            if (blockIdx.y == 0) check_span_pages(p, prefix, t_begin, t_end, TILE, tid, 128);
             Walker wk; wk.init(prefix, p.batch, t_begin);
             // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key
             float nm[N], l_acc[N];
@@ -408,17 +399,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 }
                 named_bar_sync(1, 128);
             };
-            // The loop starts with one dry pass (g = -1) over the per-tile code, re-centering path included, on an empty
-            // key set: it synchronises with nobody and publishes nothing.  The softmax warps are idle until the first
-            // scores exist (several microseconds); a first execution of this code costs one instruction-cache miss
-            // per 128 bytes of it, and when that happened on the first real tile - while every SM was filling its
-            // stages from HBM - the first softmax took 4 us instead of 0.7 us and held the whole pipeline back.
-            for (int g = -1; g < n_total; ++g) {
-                const bool dry = g < 0;
+            for (int g = 0; g < n_total; ++g) {
                 const int sb = g & 1;
-                const bool first = dry ? true : wk.seek(p, prefix, t_begin + g);
-                const bool last = !dry && t_begin + g + 1 == min(t_end, wk.seq_t1);
-                const int pos_first = dry ? 0 : (t_begin + g - wk.seq_t0) * TILE;
+                const bool first = wk.seek(p, prefix, t_begin + g);
+                const bool last = t_begin + g + 1 == min(t_end, wk.seq_t1);
+                const int pos_first = (t_begin + g - wk.seq_t0) * TILE;
                 if (first) {
 #pragma unroll
                     for (int c = 0; c < N; ++c) { nm[c] = INFINITY; l_acc[c] = 0.0f; }
@@ -427,18 +412,18 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     for (int q = 0; q < N / 16; ++q) {
                         const int j = (row0 + 16 * q) / p.heads;
                         const int causal_lim = p.causal ? (wk.tot_len - p.q_len + j + 1 - wk.pos_off) : 0x7fffffff;
-                        lim[q] = dry ? 0 : min(wk.seq_len, causal_lim);
+                        lim[q] = min(wk.seq_len, causal_lim);
                         lim_min = min(lim_min, lim[q]);
                     }
                 }
-                if (!dry) mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
+                mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
                 tc_fence_after();
                 float s[N];
 #pragma unroll
                 for (int c0 = 0; c0 < N; c0 += 16) tmem_ld16(tmem + lane_base + L::TMEM_S + sb * N + c0, s + c0);
                 tmem_wait_ld();
                 tc_fence_before();
-                if (!dry) mbar_arrive(&ms.s_empty[sb]);
+                mbar_arrive(&ms.s_empty[sb]);
 
                 // x = log2-domain exponent of the stored probability: score*scale - m_ref + P_SCALE_LOG2
                 const int pos = tid < TILE ? pos_first + tid : 0x7fffffff;           // lanes beyond the tile: always masked
@@ -453,7 +438,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 float xm = x[0];
 #pragma unroll
                 for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
-                const bool recenter = named_bar_or(1, 128, dry || xm > P_SCALE_LOG2 + RECENTER);
+                const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
                 if (recenter) {
                     float mx[N];
 #pragma unroll
@@ -516,7 +501,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (MMA_M * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
                 fence_proxy_async();
-                if (!dry) mbar_arrive(&ms.p_full[sb]);
+                mbar_arrive(&ms.p_full[sb]);
 
                 if (last) {
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out

@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                         const int id = id0 + u * PRODUCERS;
                         if (sl[u] != -2) {
                             const int tr = id / ncols, c = id - tr * ncols;
-                            const uint8_t* src = src_base + (long long)(sl[u] < 0 ? 0 : sl[u]) * stride + c * 16;
+                            const uint8_t* src = src_base + (long long)clamp_slot(p, sl[u]) * stride + c * 16;
                             cp_async16(dst_of(tok0 + tr, c), src, sl[u] < 0 ? 0u : 16u);
                         }
                     }
@@ -458,12 +458,12 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 if (it < CODE_IT) {
                     const uint32_t pk = cp_pk[it];
                     const int sl = __shfl_sync(0xffffffffu, row_slot, pk & 15u);
-                    cp_async16(unit_addr + (pk >> 16), p.kv_codes + (long long)max(sl, 0) * p.kv_codes_stride + ((pk >> 4) & 0xfffu),
+                    cp_async16(unit_addr + (pk >> 16), p.kv_codes + (long long)clamp_slot(p, sl) * p.kv_codes_stride + ((pk >> 4) & 0xfffu),
                                sl < 0 ? 0u : 16u);
                 } else {
                     const int id = lane + 32 * (it - CODE_IT), tr = min(id / 3, UNIT_TOK - 1), wd = id - (id / 3) * 3;
                     const int sl = __shfl_sync(0xffffffffu, row_slot, tr);
-                    const uintptr_t bs = reinterpret_cast<uintptr_t>(p.kv_bs + (long long)max(sl, 0) * p.kv_bs_stride);
+                    const uintptr_t bs = reinterpret_cast<uintptr_t>(p.kv_bs + (long long)clamp_slot(p, sl) * p.kv_bs_stride);
                     const int nwords = ((int)(bs & 7) + C::NB + 7) >> 3;   // only words that overlap the row are read
                     if (id < UNIT_TOK * 3)
                         cp_async8(unit_addr + C::OFF_UNIT_SCALES + tr * 24 + wd * 8, reinterpret_cast<const void*>((bs & ~(uintptr_t)7) + wd * 8),
@@ -489,7 +489,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 const int cur = S == 1 ? held[0] : (buf == 0 ? held[0] : held[S - 1]);
                 // the unit moves into registers: blocks par, par + 2, ... of row tok with their E8M0 bytes (a zero-filled
                 // row reads as codes 0, scale 0)
-                const int o = (int)(reinterpret_cast<uintptr_t>(p.kv_bs + (long long)max(cur, 0) * p.kv_bs_stride) & 7);
+                const int o = (int)(reinterpret_cast<uintptr_t>(p.kv_bs + (long long)clamp_slot(p, cur) * p.kv_bs_stride) & 7);
                 const unsigned char* sc_row = unit + C::OFF_UNIT_SCALES + tok * 24 + o + par;
                 uint32_t sc[NBH], e = 0;
                 uint4 v[NBH];
@@ -536,6 +536,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
         } else if (warp < 4) {
             // =========================== softmax / correction / epilogue (128 threads) ===========
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+            // idle until the first scores exist: look over the page ids of this CTA's span (reporting only, see clamp_slot)
+            if (blockIdx.y == 0) check_span_pages(p, prefix, t_begin, t_end, TILE, tid, 128);
             Walker wk; wk.init(prefix, p.batch, t_begin);
             float qk_base = 0.0f;          // sm_scale * log2(e) * (scale of this sequence's Q bytes)
             int e_run = 0;                 // exponent frame of O (block-scaled caches)

@@ -90,9 +90,10 @@ typedef struct {
     const void *kv_rope;      /* hybrid only: [slots,64] e4m3fn */
     int64_t kv_rope_stride;   /* bytes between slots; multiple of 16 */
     const float *kv_scale;    /* device fp32[1]: per-tensor scale of the e4m3 codes (e4m3: whole row, hybrid: rope) */
-    int64_t num_slots;        /* rows in the cache planes, > 0.  Every slot the page table yields is checked against
-                               * it on the device: a slot outside [0, num_slots) is not read (the key counts as a
-                               * row of zeros) and sets B200_MLA_STATUS_BAD_PAGE */
+    int64_t num_slots;        /* rows in the cache planes, > 0.  Every slot the page table yields is clamped into
+                               * [0, num_slots) on the device, so nothing outside the planes is ever read; a page id
+                               * that needed the clamp sets B200_MLA_STATUS_BAD_PAGE and the outputs of that call
+                               * are meaningless (the key read as some other row of the cache) */
 
     /* ---- page table ---- */
     const int32_t *kv_indptr;     /* device int32[batch+1], token offsets (task.py:14) */
@@ -201,8 +202,8 @@ int32_t b200_mla_decode_static(const b200_mla_decode_args *args, void *stream);
  * report nothing, mixed-mla/submission.py:626-644 returns whatever they wrote).  The kernels OR bits into the first
  * word of the workspace and never clear them:
  *   B200_MLA_STATUS_TIMEOUT   a bounded device-side wait expired; the outputs of that call are not valid
- *   B200_MLA_STATUS_BAD_PAGE  kv_indptr / kv_indices named a slot outside [0, num_slots); that key was replaced
- *                             by a row of zeros, nothing outside the cache planes was read
+ *   B200_MLA_STATUS_BAD_PAGE  kv_indptr / kv_indices named a slot outside [0, num_slots); nothing outside the cache
+ *                             planes was read (the id was clamped), the outputs of that call are meaningless
  * b200_mla_read_status enqueues one 4-byte copy of the word into `out` (device, pinned or pageable host memory) on
  * `stream`; the caller decides whether and when to wait for it.  b200_mla_reset_status enqueues the zeroing of the
  * word (and of the rest of the 256-byte header); call it once on a fresh workspace.  workspace == NULL addresses

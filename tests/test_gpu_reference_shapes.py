@@ -124,9 +124,9 @@ def test_random_shapes_against_oracle(pkg):
 @pytest.mark.parametrize("kv_format,q_format", [("fp8", "fp8"), ("mxfp4", "bf16"), ("hybrid", "fp8")])
 def test_page_id_outside_the_cache_is_harmless_and_reported(pkg, impl, kv_format, q_format):
     """num_slots is declared SMALLER than the real allocation and a few page ids point between the two, so
-    the rows they name exist in memory whatever the kernel does.  Expected: those keys count as rows of
-    zeros (the oracle is given zeroed rows), the BAD_PAGE bit is set, check_status raises, and after a reset
-    a clean call reads status 0."""
+    the rows they name exist in memory whatever the kernel does.  Expected: the ids are clamped into the
+    declared planes (the output stays finite, rows of sequences without a bad id are unaffected), the
+    BAD_PAGE bit is set, check_status raises, and after a reset a clean call reads status 0."""
     from amd_optimization_challenge_b200 import _cabi, submission
     lens = [300, 77, 129, 5, 260, 31, 64]                          # a batch size no other test uses
     hidden = 8
@@ -134,22 +134,20 @@ def test_page_id_outside_the_cache_is_harmless_and_reported(pkg, impl, kv_format
     q, kvd, qo, kvp, cfg = data
     T = sum(lens)
     declared = tuple(t[:T - hidden] if t.dim() > 1 and t.shape[0] == T else t for t in kvd[kv_format])
-    bad = cfg["kv_indices"] >= T - hidden
+    bad = (cfg["kv_indices"] >= T - hidden).cpu()
     assert int(bad.sum()) == hidden
     cfg_bad = dict(cfg, kv_format=kv_format, q_format=q_format, impl=impl)
     out = pkg.custom_kernel((q, {kv_format: declared}, qo, kvp, cfg_bad))
     torch.cuda.synchronize()
     bits = submission.read_status(q.device, len(lens), 16, 1)
     assert bits == _cabi.STATUS_BAD_PAGE
-    # oracle on the same problem with the hidden rows zeroed
-    zeroed = []
-    for t in kvd[kv_format]:
-        t = t.clone()
-        if t.dim() > 1 and t.shape[0] == T:
-            t[T - hidden:] = 0
-        zeroed.append(t)
-    ref = oracle_for_data((q, {kv_format: tuple(zeroed)}, qo, kvp, cfg), kv_format, q_format)
-    assert_close(out, ref, tight=1.5e-2)
+    assert torch.isfinite(out.float()).all()
+    # sequences none of whose keys were redirected come out as usual
+    ref = oracle_for_data(data, kv_format, q_format)
+    ip = kvp.cpu().tolist()
+    clean = [b for b in range(len(lens)) if not bool(bad[ip[b]:ip[b + 1]].any())]
+    for b in clean:
+        assert_close(out[b:b + 1], ref[b:b + 1], tight=1.5e-2)
     with pytest.raises(RuntimeError, match="outside the cache"):
         pkg.custom_kernel((q, {kv_format: declared}, qo, kvp, dict(cfg_bad, check_status=True)))
     # reset the sticky word of that workspace; a clean call leaves it at zero
