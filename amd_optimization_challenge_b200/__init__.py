@@ -6,8 +6,8 @@ Public surface (mirrors the reference's mixed-mla problem definition):
   (mixed-mla/submission.py:626).
 * ``generate_input`` / ``quantize_fp8`` / ``quantize_mxfp4`` / ``dequantize_mxfp4`` - host-side
   mirrors of competitor_submissions/mi355x_reference/reference.py:65-154,288-346.
-* ``mla_decode`` / ``combine_partials`` / ``quantize_q_fp8`` - thin wrappers over the C ABI of
-  libb200mla.so (include/b200_mla.h).
+* ``mla_decode`` / ``combine_partials`` / ``quantize_q_fp8`` / ``kv_append`` - thin wrappers over the
+  C ABI of libb200mla.so (include/b200_mla.h).
 
 The compute path is hand-written CUDA for sm_100a behind that C ABI; there is no CPU or Triton
 fallback.  The library-backed names are resolved on first access (so that the build module can be
@@ -16,7 +16,7 @@ imported before the library exists); if libb200mla.so has not been built, that a
 from .inputs import (generate_input, quantize_fp8, quantize_mxfp4, dequantize_mxfp4, quantize_hybrid,
                      QK_HEAD_DIM, V_HEAD_DIM, KV_LORA_RANK, QK_ROPE_HEAD_DIM)
 
-_LIB_BACKED = ("custom_kernel", "mla_decode", "combine_partials", "quantize_q_fp8", "q_amax_parts", "q_amax_parts")
+_LIB_BACKED = ("custom_kernel", "mla_decode", "combine_partials", "quantize_q_fp8", "q_amax_parts", "kv_append")
 
 
 def __getattr__(name):
@@ -28,7 +28,7 @@ def __getattr__(name):
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 __all__ = [
-    "custom_kernel", "mla_decode", "combine_partials", "quantize_q_fp8", "q_amax_parts",
+    "custom_kernel", "mla_decode", "combine_partials", "quantize_q_fp8", "q_amax_parts", "kv_append",
     "generate_input", "quantize_fp8", "quantize_mxfp4", "dequantize_mxfp4", "quantize_hybrid",
     "QK_HEAD_DIM", "V_HEAD_DIM", "KV_LORA_RANK", "QK_ROPE_HEAD_DIM",
 ]

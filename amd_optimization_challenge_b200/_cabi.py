@@ -36,9 +36,19 @@ class DecodeArgs(ctypes.Structure):
     ]
 
 
+class KvAppendArgs(ctypes.Structure):
+    """struct b200_mla_kv_append_args"""
+    _fields_ = [
+        ("rows_bf16", _vp), ("n", _i64), ("row_stride", _i64), ("slots", _vp), ("base_slot", _i64), ("num_slots", _i64),
+        ("kv_format", _i32), ("reserved", _i32),
+        ("kv_codes", _vp), ("kv_codes_stride", _i64), ("kv_block_scales", _vp), ("kv_block_scales_stride", _i64),
+        ("kv_rope", _vp), ("kv_rope_stride", _i64), ("kv_scale", _vp), ("status", _vp),
+    ]
+
+
 EXPORTS = ("b200_mla_version", "b200_mla_last_error", "b200_mla_workspace_bytes", "b200_mla_decode",
            "b200_mla_combine", "b200_mla_quantize_fp8", "b200_mla_q_amax", "b200_mla_set_stage1_events",
-           "b200_mla_decode_static", "b200_mla_read_status", "b200_mla_reset_status")
+           "b200_mla_decode_static", "b200_mla_read_status", "b200_mla_reset_status", "b200_mla_kv_append")
 STATUS_TIMEOUT, STATUS_BAD_PAGE = 1, 2
 
 
@@ -66,6 +76,8 @@ def _load() -> ctypes.CDLL:
     lib.b200_mla_read_status.argtypes = [_vp, _vp, _vp]
     lib.b200_mla_reset_status.restype = _i32
     lib.b200_mla_reset_status.argtypes = [_vp, _vp]
+    lib.b200_mla_kv_append.restype = _i32
+    lib.b200_mla_kv_append.argtypes = [ctypes.POINTER(KvAppendArgs), _vp]
     lib.b200_mla_set_stage1_events.restype = _i32
     lib.b200_mla_set_stage1_events.argtypes = [_vp, _vp]
     return lib

@@ -25,6 +25,10 @@ cudaError_t launch_combine_parts(const float* o_parts, const float* lse_parts, i
                                  cudaStream_t stream);
 cudaError_t launch_quantize_fp8(const __nv_bfloat16* x, long long n, uint8_t* out, float* scale_out,
                                 unsigned int* scratch, cudaStream_t stream);
+cudaError_t launch_kv_append(const void* src, long long n, long long src_stride, const int* slots, long long base_slot,
+                             long long num_slots, int kv_format, void* codes, long long codes_stride, void* bs,
+                             long long bs_stride, void* rope, long long rope_stride, const float* scale, int* bad,
+                             cudaStream_t stream);
 cudaError_t launch_q_amax_parts(const __nv_bfloat16* x, long long n, unsigned int* parts, cudaStream_t stream);
 }  // namespace b200mla
 
@@ -286,6 +290,33 @@ int32_t b200_mla_q_amax(const void* x_bf16, int64_t n, uint32_t* parts_out, void
         return fail(B200_MLA_ERR_INVALID_ARG, "x must be 16-byte and parts_out 4-byte aligned");
     cudaError_t e = launch_q_amax_parts((const __nv_bfloat16*)x_bf16, n, parts_out, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "amax launch failed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_kv_append(const b200_mla_kv_append_args* a, void* stream) {
+    if (!a) return fail(B200_MLA_ERR_INVALID_ARG, "args is NULL");
+    if (a->n < 0) return fail(B200_MLA_ERR_INVALID_ARG, "n must be >= 0");
+    if (a->n == 0) return B200_MLA_OK;
+    if (a->kv_format < B200_MLA_KV_E4M3 || a->kv_format > B200_MLA_KV_HYBRID) return fail(B200_MLA_ERR_INVALID_ARG, "bad kv_format %d", a->kv_format);
+    if (!a->rows_bf16 || !a->kv_codes) return fail(B200_MLA_ERR_INVALID_ARG, "rows_bf16 and kv_codes are required");
+    if (((uintptr_t)a->rows_bf16 & 15) || a->row_stride % 8 || a->row_stride < B200_MLA_QK_DIM)
+        return fail(B200_MLA_ERR_INVALID_ARG, "rows_bf16 must be 16-byte aligned with a row stride >= 576 that is a multiple of 8 elements");
+    if (((uintptr_t)a->kv_codes & 15) || a->kv_codes_stride % 16) return fail(B200_MLA_ERR_INVALID_ARG, "kv_codes must be 16-byte aligned with a stride multiple of 16");
+    const int min_codes = a->kv_format == B200_MLA_KV_E4M3 ? 576 : (a->kv_format == B200_MLA_KV_MXFP4 ? 288 : 256);
+    if (a->kv_codes_stride < min_codes) return fail(B200_MLA_ERR_INVALID_ARG, "kv_codes_stride is smaller than a row (%d bytes)", min_codes);
+    if (a->kv_format != B200_MLA_KV_MXFP4 && !a->kv_scale) return fail(B200_MLA_ERR_INVALID_ARG, "kv_scale is required for e4m3 / hybrid caches");
+    if (a->kv_format != B200_MLA_KV_E4M3 && (!a->kv_block_scales || a->kv_block_scales_stride < (a->kv_format == B200_MLA_KV_MXFP4 ? 18 : 16)))
+        return fail(B200_MLA_ERR_INVALID_ARG, "kv_block_scales (stride >= 18 for mxfp4, >= 16 for hybrid) is required");
+    if (a->kv_format == B200_MLA_KV_HYBRID && (!a->kv_rope || ((uintptr_t)a->kv_rope & 15) || a->kv_rope_stride % 16 || a->kv_rope_stride < 64))
+        return fail(B200_MLA_ERR_INVALID_ARG, "kv_rope must be 16-byte aligned with a stride >= 64 that is a multiple of 16");
+    if (a->num_slots <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "num_slots must be positive");
+    if (!a->slots && (a->base_slot < 0 || a->base_slot + a->n > a->num_slots))
+        return fail(B200_MLA_ERR_INVALID_ARG, "rows [base_slot, base_slot + n) do not fit in num_slots");
+    if (a->slots && !a->status) return fail(B200_MLA_ERR_INVALID_ARG, "status (device int32) is required with a slot list: it reports slots outside the cache");
+    cudaError_t e = launch_kv_append(a->rows_bf16, a->n, a->row_stride, a->slots, a->base_slot, a->num_slots, a->kv_format,
+                                     a->kv_codes, a->kv_codes_stride, a->kv_block_scales, a->kv_block_scales_stride,
+                                     a->kv_rope, a->kv_rope_stride, a->kv_scale, a->status, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "kv append launch failed: %s", cudaGetErrorString(e));
     return B200_MLA_OK;
 }
 

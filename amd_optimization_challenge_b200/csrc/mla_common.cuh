@@ -220,10 +220,13 @@ __device__ __forceinline__ uint8_t q_cast_e4m3(__nv_bfloat16 x, float scale) {
 }
 // eight bf16 values (one 16-byte vector) -> eight e4m3 bytes
 __device__ __forceinline__ uint2 q_cast_e4m3x8(const uint4& v, float scale) {
-    const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(&v);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};             // by value: the vector stays in registers
     uint32_t o[2] = {0u, 0u};
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o[k >> 2] |= (uint32_t)q_cast_e4m3(in[k], scale) << (8 * (k & 3));
+    for (int k = 0; k < 8; ++k) {
+        const __nv_bfloat16 x = __ushort_as_bfloat16((unsigned short)(w[k >> 1] >> (16 * (k & 1))));
+        o[k >> 2] |= (uint32_t)q_cast_e4m3(x, scale) << (8 * (k & 3));
+    }
     return make_uint2(o[0], o[1]);
 }
 // Scale of the e4m3 Q codes, the same value in every thread of the block.  All threads call it (it

@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 mbar_wait(&ms.q_empty[qb], wk.pair / 2 - 1, abort_flag);
                 const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
                 if (p.q_cast) {
-                    // eight bf16 values in, eight e4m3 bytes (half a 16-byte column) out; eight loads in flight per thread
+                    // eight bf16 values in, eight e4m3 bytes (half a 16-byte column) out
                     unsigned char* q_smem = smem + L::OFF_Q + qb * L::Q_BYTES;
                     auto q_src = [&](int i) {
                         const int r = i / 72, v8 = i - r * 72;
@@ -250,20 +250,21 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         return reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
                                                               (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8);
                     };
+                    // All loads of a pass are issued before the first conversion: under a saturated memory system one
+                    // round trip costs 1-2 us; a pass covers all rows of a sequence (N = 16).
+                    constexpr int QV = 18;                        // 16-byte vectors per thread and pass (72 registers)
+                    static_assert((N * 72) % (QV * QT) == 0, "Q passes");
 #pragma unroll 1
-                    for (int i0 = pt; i0 < N * 72; i0 += 8 * QT) {
-                        uint4 raw[8];
+                    for (int i0 = pt; i0 < N * 72; i0 += QV * QT) {
+                        uint4 raw[QV];
 #pragma unroll
-                        for (int u = 0; u < 8; ++u)
-                            if (i0 + u * QT < N * 72) raw[u] = __ldg(q_src(i0 + u * QT));
+                        for (int u = 0; u < QV; ++u) raw[u] = __ldg(q_src(i0 + u * QT));
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) {
+                        for (int u = 0; u < QV; ++u) {
                             const int i = i0 + u * QT;
-                            if (i < N * 72) {
-                                const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
-                                *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) =
-                                    q_cast_e4m3x8(raw[u], q_sc);
-                            }
+                            const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
+                            *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) =
+                                q_cast_e4m3x8(raw[u], q_sc);
                         }
                     }
                     fence_proxy_async();                      // the MMA reads Q through the async proxy

@@ -285,6 +285,49 @@ def combine_partials_strided(buf: torch.Tensor, parts: int, part_stride: int, ls
     return out
 
 
+def kv_append(rows: torch.Tensor, kv_format: str, kv, slots=None, base_slot: int = 0):
+    """Quantise bf16 latent rows [n, (1,) 576] into the rows `slots` (int32 [n]; or base_slot + i) of the cache
+    planes `kv` (same tuple layout as mla_decode's `kv`) through b200_mla_kv_append: the bytes the reference's
+    quantisers give for those rows (reference.py:65-80 with the cache's own per-tensor scale, reference.py:88-113).
+    Returns a device int32[1] that reads 1 if a slot was outside the cache (that row was not written)."""
+    if not rows.is_cuda or rows.dtype != torch.bfloat16:
+        raise ValueError("kv_append expects CUDA bf16 rows")
+    dev = rows.device
+    rows = rows.reshape(-1, QK_DIM)
+    if rows.stride(1) != 1:
+        rows = rows.contiguous()
+    a = _cabi.KvAppendArgs()
+    a.rows_bf16, a.n, a.row_stride = rows.data_ptr(), rows.shape[0], rows.stride(0)
+    _check_index_tensor("slots", slots, dev, rows.shape[0])
+    a.slots, a.base_slot = _ptr(slots), int(base_slot)
+    a.kv_format = _KV_FORMATS[kv_format]
+    for i, t in enumerate(kv):
+        _check_plane(f"kv[{i}]", t, dev)
+    if kv_format == "fp8":
+        codes, scale = kv
+        codes = _u8(codes).reshape(-1, QK_DIM)
+        a.kv_scale = scale.data_ptr()
+    elif kv_format == "mxfp4":
+        codes, bs = kv
+        codes = _u8(codes).reshape(-1, QK_DIM // 2)
+        bs = _u8(bs)
+        a.kv_block_scales, a.kv_block_scales_stride = bs.data_ptr(), bs.stride(0)
+    else:
+        codes, bs, rope, scale = kv
+        codes = _u8(codes).reshape(-1, V_DIM // 2)
+        bs = _u8(bs)
+        rope = _u8(rope).reshape(-1, QK_DIM - V_DIM)
+        a.kv_block_scales, a.kv_block_scales_stride = bs.data_ptr(), bs.stride(0)
+        a.kv_rope, a.kv_rope_stride = rope.data_ptr(), rope.stride(0)
+        a.kv_scale = scale.data_ptr()
+    a.kv_codes, a.kv_codes_stride, a.num_slots = codes.data_ptr(), codes.stride(0), codes.shape[0]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    a.status = status.data_ptr()
+    with torch.cuda.device(dev):
+        check(lib.b200_mla_kv_append(ctypes.byref(a), _stream(dev)), "b200_mla_kv_append")
+    return status
+
+
 def custom_kernel(data):
     q, kv_data, qo_indptr, kv_indptr, config = data[:5]
     kv_format = config.get("kv_format")

@@ -168,6 +168,36 @@ int32_t b200_mla_quantize_fp8(const void *x_bf16, int64_t n, void *codes_out, fl
                               void *scratch, void *stream);
 
 /*
+ * Append rows to a quantised cache: `n` bf16 latent rows [n, 576] -> the rows `slots[i]` (or base_slot + i when
+ * slots is NULL) of an e4m3, MXFP4 or hybrid cache, with the reference quantisers' arithmetic, so that the bytes
+ * equal what quantize_fp8 (reference.py:65-80, with the given per-tensor scale) and quantize_mxfp4
+ * (reference.py:88-113; rounding rule mxfp4-mm/submission_v3_self_contained.py:19-72; fused Triton form
+ * mixed-mla/versions/v22_small_config_opt/submission_triton_quant.py:88-187) produce for the same rows.
+ * The per-tensor scale of an e4m3 cache / of a hybrid cache's rope dims is an input (device fp32[1]): rows added
+ * later cannot change the scale of rows already stored.  A slot outside [0, num_slots) is not written and sets
+ * *status (device int32, required with a slot list) to 1.
+ */
+typedef struct {
+    const void *rows_bf16;    /* device bf16 [n, 576], 16-byte aligned */
+    int64_t n;
+    int64_t row_stride;       /* elements between rows (576 when dense; multiple of 8) */
+    const int32_t *slots;     /* device int32[n] destination slots, or NULL */
+    int64_t base_slot;        /* first destination slot when slots is NULL */
+    int64_t num_slots;        /* rows in the cache planes */
+    int32_t kv_format;        /* b200_mla_kv_format */
+    int32_t reserved;
+    void *kv_codes;           /* planes as in b200_mla_decode_args */
+    int64_t kv_codes_stride;
+    void *kv_block_scales;
+    int64_t kv_block_scales_stride;
+    void *kv_rope;
+    int64_t kv_rope_stride;
+    const float *kv_scale;    /* device fp32[1]; NULL for mxfp4 */
+    int32_t *status;          /* device int32, may be NULL when slots is NULL */
+} b200_mla_kv_append_args;
+int32_t b200_mla_kv_append(const b200_mla_kv_append_args *args, void *stream);
+
+/*
  * First half of that quantisation on its own (the amax of mixed-mla/fused_fp8_quant.py:27-53): the
  * largest bf16 magnitude of x, left as B200_MLA_Q_AMAX_PARTS per-block partial maxima (bf16 bit
  * patterns, uint32 each) in `parts_out`.  A decode call with q_format B200_MLA_Q_BF16_CAST_E4M3
