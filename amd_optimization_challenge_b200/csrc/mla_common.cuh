@@ -80,9 +80,13 @@ __device__ __forceinline__ int seq_of_unit(const int* prefix, int batch, int u) 
     return lo;
 }
 // First tile of CTA w's span (w = G gives the total number of tiles).
-__device__ __forceinline__ int span_begin(const int* prefix, int batch, int w, int G) {
+// Not inlined: every stage-1 CTA calls it twice right after launch, and code that runs for the first time costs an
+// instruction-cache miss per 128 bytes; the 64-bit division is only taken where the product needs it.
+static __device__ __noinline__ int span_begin(const int* prefix, int batch, int w, int G) {
     if (w >= G) return prefix[batch];
-    const int u = (int)(((long long)w * total_units(prefix[batch], batch)) / G);
+    const int tu = total_units(prefix[batch], batch);
+    const int u = ((unsigned long long)(unsigned)w * (unsigned)tu >> 32) == 0 ? (int)(((unsigned)w * (unsigned)tu) / (unsigned)G)
+                                                                            : (int)(((long long)w * tu) / G);
     const int b = seq_of_unit(prefix, batch, u);
     return max(prefix[b], u - SEQ_UNITS * (b + 1));
 }
@@ -212,20 +216,41 @@ __device__ __forceinline__ float q_scale_from_amax_bits(unsigned int bits) {
     amax = __bfloat162float(__float2bfloat16_rn(fmaxf(amax, 1e-12f)));
     return __bfloat162float(__float2bfloat16_rn(amax / 448.0f));
 }
+// x / scale rounded to bf16, as a float: the reference divides two bf16 tensors, i.e. an IEEE fp32 division whose
+// result is rounded to bf16.  Evaluated without a division: t = x * r with r = RN(1 / scale), one exact residual
+// and one correction (Markstein) give the correctly rounded fp32 quotient; checked exhaustively on the CPU against
+// x / scale for every finite bf16 x and every positive normal bf16 scale (identical after the bf16 rounding and the
+// clamp to +-448).  The sign is taken from x, so that -0 stays -0.
+__device__ __forceinline__ float q_quotient_bf16(float x, float scale, float rscale) {
+    const float t = x * rscale;
+    float y = fmaf(fmaf(-t, scale, x), rscale, t);
+    if (!(fabsf(t) <= 3.0e38f)) y = t;                                        // infinite / NaN input
+    y = copysignf(fabsf(y), x);
+    return __bfloat162float(__float2bfloat16_rn(y));
+}
 __device__ __forceinline__ uint8_t q_cast_e4m3(__nv_bfloat16 x, float scale) {
-    float y = __bfloat162float(x) / scale;                                   // IEEE division
-    y = __bfloat162float(__float2bfloat16_rn(y));                            // bf16 rounding of the quotient
-    y = fminf(fmaxf(y, -448.0f), 448.0f);
+    const float y = fminf(fmaxf(q_quotient_bf16(__bfloat162float(x), scale, __frcp_rn(scale)), -448.0f), 448.0f);
     return (uint8_t)__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
 }
 // eight bf16 values (one 16-byte vector) -> eight e4m3 bytes
 __device__ __forceinline__ uint2 q_cast_e4m3x8(const uint4& v, float scale) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};             // by value: the vector stays in registers
-    uint32_t o[2] = {0u, 0u};
+    const float r = __frcp_rn(scale);
+    uint32_t o[2];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const __nv_bfloat16 x = __ushort_as_bfloat16((unsigned short)(w[k >> 1] >> (16 * (k & 1))));
-        o[k >> 2] |= (uint32_t)q_cast_e4m3(x, scale) << (8 * (k & 3));
+    for (int h = 0; h < 2; ++h) {
+        float y[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t word = w[2 * h + (k >> 1)];
+            const float x = __uint_as_float((k & 1) ? (word & 0xffff0000u) : (word << 16));   // bf16 -> fp32
+            y[k] = q_quotient_bf16(x, scale, r);
+        }
+        // the conversion saturates to +-448, which is the reference's clamp
+        uint16_t lo16, hi16;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo16) : "f"(y[0]), "f"(y[1]));
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi16) : "f"(y[2]), "f"(y[3]));
+        o[h] = (uint32_t)lo16 | ((uint32_t)hi16 << 16);
     }
     return make_uint2(o[0], o[1]);
 }

@@ -17,8 +17,7 @@
 //
 // Roles:  warps 0-3  softmax / correction / epilogue (one TMEM lane = one token / one output dim per thread)
 //         warp  4    tcgen05.mma issue (one lane, event driven), TMEM allocation
-//         warps 5-6  Q rows of each sequence (copy, or load + per-tensor e4m3 quantisation of a bf16 Q)
-//         warps 7..  paged gather: 16-byte cp.async of cache rows through the page table
+//         warps 5..  paged gather: 16-byte cp.async of cache rows (and of Q) through the page table
 //                    straight into the 128B-swizzled UMMA layout, completion signalled on an mbarrier.
 // Movers measured on B200 for shuffled 576-byte rows, device-wide, one CTA per SM:
 //         16-byte cp.async (LSU)                       3.5 - 4.4 TB/s, lands directly in operand layout
@@ -61,8 +60,7 @@ struct Layout {
     static constexpr int NPANEL = 5;                             // Q keeps five 128-byte-wide panels
         static constexpr int PRODUCER_WARPS = (N == 16) ? 9 : 2;     // N = 16: 288 = 8 x 36 threads, one 16-byte column and one row phase each; N = 32 needs the registers
     static constexpr int PRODUCERS = 32 * PRODUCER_WARPS;
-    static constexpr int Q_THREADS = 64;                          // two warps load (and cast) the Q rows of each sequence
-    static constexpr int FIRST_PRODUCER = 160 + Q_THREADS;
+    static constexpr int FIRST_PRODUCER = 160;
     static constexpr int THREADS = FIRST_PRODUCER + PRODUCERS;
     static constexpr int Q_PANEL_BYTES = N * 128;
     static constexpr int Q_BYTES = NPANEL * Q_PANEL_BYTES;        // one Q buffer (two of them: next sequence's Q loads early)
@@ -84,7 +82,7 @@ struct Misc {
     unsigned int q_amax;         // block_q_scale's word
     uint64_t slot_full[SLOT_RING];
     int slot[SLOT_RING][MMA_M];  // page ids of the tiles g .. g + NS, fetched by 4-byte cp.async
-    float red[4][32];            // cross-warp exchange (max / sum), 32 = max N
+    __align__(16) float red[4][32];   // cross-warp exchange (max / sum), 32 = max N
 };
 
 template <int N>
@@ -116,7 +114,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128);
             mbar_init(&ms.p_full[i], 128); mbar_init(&ms.p_empty[i], 1);
-            mbar_init(&ms.q_full[i], L::Q_THREADS); mbar_init(&ms.q_empty[i], 1);
+            mbar_init(&ms.q_full[i], PRODUCERS); mbar_init(&ms.q_empty[i], 1);
         }
         for (int i = 0; i < SLOT_RING; ++i) mbar_init(&ms.slot_full[i], PRODUCERS);
         mbar_init(&ms.o_free, 128);
@@ -138,7 +136,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
-        if (warp >= 7) {
+        if (warp >= 5) {
             // =========================== gather ===========================
             // One stage = TILE tokens x 36 sixteen-byte columns.  Consecutive threads take consecutive
             // columns, so a warp instruction reads 512 contiguous bytes of (at most two) rows.
@@ -172,11 +170,84 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 const int id = ms.slot[g % SLOT_RING][tok];
                 return p.page_size == 1 ? id : id * p.page_size + (pos % p.page_size);
             };
+            // Q of the (CTA, sequence) pair that has been loaded but not yet stored: sequence, pair index, tile at which to store
+            constexpr int QV = (N * 72 + PRODUCERS - 1) / PRODUCERS;     // 16-byte bf16 vectors per thread
+            constexpr bool Q_PRELOAD = QV <= 8;
+            uint4 qv[Q_PRELOAD ? QV : 1];
+            int q_b = 0, q_pair = 0, q_due = -1;
+            auto q_src = [&](int b, int i) {
+                const int r = i / 72, v8 = i - r * 72;
+                const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                return reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                                                      (long long)(b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8);
+            };
+            // Q rows of sequence q_b -> swizzled K-major panels of Q buffer (q_pair & 1)
+            auto flush_q = [&]() {
+                const int qb = q_pair & 1;
+                mbar_wait(&ms.q_empty[qb], q_pair / 2 - 1, abort_flag);
+                const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
+                if (p.q_cast) {
+                    // bf16 rows, quantised here: eight values in, eight e4m3 bytes (half a 16-byte column) out
+                    unsigned char* q_smem = smem + L::OFF_Q + qb * L::Q_BYTES;
+                    auto put = [&](int i, const uint4& raw) {
+                        const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
+                        *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) =
+                            q_cast_e4m3x8(raw, q_sc);
+                    };
+                    if (Q_PRELOAD) {
+#pragma unroll
+                        for (int k = 0; k < QV; ++k) {
+                            const int i = pt + k * PRODUCERS;
+                            if (i < N * 72) put(i, qv[Q_PRELOAD ? k : 0]);
+                        }
+                    } else {
+                        for (int i0 = pt; i0 < N * 72; i0 += 8 * PRODUCERS) {     // eight loads in flight, then their conversion
+                            uint4 raw[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+                                if (i0 + u * PRODUCERS < N * 72) raw[u] = __ldg(q_src(q_b, i0 + u * PRODUCERS));
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+                                if (i0 + u * PRODUCERS < N * 72) put(i0 + u * PRODUCERS, raw[u]);
+                        }
+                    }
+                    fence_proxy_async();                      // the MMA reads Q through the async proxy
+                    mbar_arrive(&ms.q_full[qb]);
+                } else {
+                    for (int i = pt; i < N * 36; i += PRODUCERS) {
+                        const int r = i / 36, c = i - r * 36;
+                        const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
+                        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
+                                             (long long)(q_b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
+                        cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
+                    }
+                    cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
+                }
+                q_due = -1;
+            };
 #pragma unroll 1
             for (int g = 0; g < NS; ++g) prefetch_ids(g);
             for (int g = 0; g < n_total; ++g) {
                 const int st = g % NS;
-                wk.seek(p, prefix, t_begin + g);
+                const bool first = wk.seek(p, prefix, t_begin + g);
+                // Q rows of a new sequence.  A bf16 Q that is quantised on load is fetched into registers NOW, ahead of the
+                // tile's copies (a load issued behind them returns only after the megabytes queued before it); it is converted
+                // and stored right after them.  (Deferring the conversion until all stages are in flight was measured: 1.3 us
+                // slower per call - three tiles requested at once make the first one land later.)
+                if (first) {
+                    if (q_due >= 0) flush_q();                   // a sequence shorter than the deferral
+                    q_b = wk.b; q_pair = wk.pair;
+                    if (p.q_cast && Q_PRELOAD) {
+#pragma unroll
+                        for (int k = 0; k < QV; ++k) {
+                            const int i = pt + k * PRODUCERS;
+                            qv[Q_PRELOAD ? k : 0] = i < N * 72 ? __ldg(q_src(q_b, i)) : make_uint4(0u, 0u, 0u, 0u);
+                        }
+                        q_due = g;
+                    } else {
+                        q_due = g;                               // copied (or loaded in batches) right after this tile
+                    }
+                }
                 const int pos0 = (t_begin + g - wk.seq_t0) * TILE;
                 if (paged) mbar_wait(&ms.slot_full[g % SLOT_RING], g / SLOT_RING, abort_flag);
                 mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
@@ -225,61 +296,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     prefetch_ids(g + NS);
                 }
                 cp_async_mbar_arrive_noinc(&ms.kv_full[st]);   // asynchronous: the thread does not wait for its copies
+                if (q_due >= 0 && (g >= q_due || g == n_total - 1)) flush_q();
             }
-            cp_async_wait_all();
-        } else if (warp >= 5) {
-            // =========================== Q rows (two warps) ===========================
-            // One pass per (CTA, sequence) pair, one pair ahead of the QK stream (two Q buffers): the rows of the sequence
-            // -> swizzled K-major panels.  e4m3 rows are copied; bf16 rows that are quantised here (per-tensor, the
-            // reference's rule) are loaded, converted and stored.  Kept off the gather warps: the conversion of one
-            // sequence's rows takes several microseconds, during which they would not request cache rows.
-            const int pt = tid - 160;
-            constexpr int QT = L::Q_THREADS;
-            Walker wk; wk.init(prefix, p.batch, t_begin);
-            for (int t = t_begin; t < t_end; t = wk.seq_t1) {
-                wk.seek(p, prefix, t);
-                const int qb = wk.pair & 1;
-                mbar_wait(&ms.q_empty[qb], wk.pair / 2 - 1, abort_flag);
-                const uint32_t q_addr = smem_base + L::OFF_Q + qb * L::Q_BYTES;
-                if (p.q_cast) {
-                    // eight bf16 values in, eight e4m3 bytes (half a 16-byte column) out
-                    unsigned char* q_smem = smem + L::OFF_Q + qb * L::Q_BYTES;
-                    auto q_src = [&](int i) {
-                        const int r = i / 72, v8 = i - r * 72;
-                        const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                        return reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
-                                                              (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + v8 * 8);
-                    };
-                    // All loads of a pass are issued before the first conversion: under a saturated memory system one
-                    // round trip costs 1-2 us; a pass covers all rows of a sequence (N = 16).
-                    constexpr int QV = 18;                        // 16-byte vectors per thread and pass (72 registers)
-                    static_assert((N * 72) % (QV * QT) == 0, "Q passes");
-#pragma unroll 1
-                    for (int i0 = pt; i0 < N * 72; i0 += QV * QT) {
-                        uint4 raw[QV];
-#pragma unroll
-                        for (int u = 0; u < QV; ++u) raw[u] = __ldg(q_src(i0 + u * QT));
-#pragma unroll
-                        for (int u = 0; u < QV; ++u) {
-                            const int i = i0 + u * QT;
-                            const int r = i / 72, v8 = i - r * 72, c = v8 >> 1;
-                            *reinterpret_cast<uint2*>(q_smem + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4) + (v8 & 1) * 8) =
-                                q_cast_e4m3x8(raw[u], q_sc);
-                        }
-                    }
-                    fence_proxy_async();                      // the MMA reads Q through the async proxy
-                    mbar_arrive(&ms.q_full[qb]);
-                } else {
-                    for (int i = pt; i < N * 36; i += QT) {
-                        const int r = i / 36, c = i - r * 36;
-                        const int rg = row0 + r, j = rg / p.heads, h = rg - j * p.heads;
-                        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q) +
-                                             (long long)(wk.b * p.q_len + j) * p.q_row_stride + (long long)h * p.q_head_stride + c * 16;
-                        cp_async16(q_addr + (c >> 3) * L::Q_PANEL_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, 16u);
-                    }
-                    cp_async_mbar_arrive_noinc(&ms.q_full[qb]);
-                }
-            }
+            // every tile has been requested and the last ones are still being multiplied: time to look over the page ids of
+            // this CTA's span (reporting only, see clamp_slot) without delaying anything
+            if (blockIdx.y == 0) check_span_pages(p, prefix, t_begin, t_end, TILE, pt, PRODUCERS);
             cp_async_wait_all();
         } else if (warp == 4) {
             // =========================== MMA issue (whole warp, one elected lane per instruction) ===========================
@@ -372,34 +393,12 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
             const float out_scale = kv_sc;
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-            // idle until the first scores exist: look over the page ids of this CTA's span (reporting only, see clamp_slot)
-            if (blockIdx.y == 0) check_span_pages(p, prefix, t_begin, t_end, TILE, tid, 128);
             Walker wk; wk.init(prefix, p.batch, t_begin);
             // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key
             float nm[N], l_acc[N];
             // token position pos is visible to the rows of 16-column chunk q iff pos < lim[q]
             // (heads is a multiple of 16, so the query index j is constant inside a chunk)
             int lim[N / 16], lim_min = 0;
-            // per-column reduction over the 128 threads; result replicated in every thread
-            auto reduce_cols = [&](float (&v)[N], bool is_max) {
-#pragma unroll
-                for (int c = 0; c < N; ++c) {
-                    float x = v[c];
-#pragma unroll
-                    for (int o = 16; o >= 1; o >>= 1) {
-                        const float y = __shfl_xor_sync(0xffffffffu, x, o);
-                        x = is_max ? fmaxf(x, y) : x + y;
-                    }
-                    if (lane == 0) ms.red[warp][c] = x;
-                }
-                named_bar_sync(1, 128);
-#pragma unroll
-                for (int c = 0; c < N; ++c) {
-                    const float a0 = ms.red[0][c], a1 = ms.red[1][c], a2 = ms.red[2][c], a3 = ms.red[3][c];
-                    v[c] = is_max ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : (a0 + a1) + (a2 + a3);
-                }
-                named_bar_sync(1, 128);
-            };
             for (int g = 0; g < n_total; ++g) {
                 const int sb = g & 1;
                 const bool first = wk.seek(p, prefix, t_begin + g);
@@ -444,7 +443,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     float mx[N];
 #pragma unroll
                     for (int c = 0; c < N; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : s[c] * score_scale;
-                    reduce_cols(mx, true);
+                    reduce_cols_128<N, true>(mx, ms.red, warp, lane, 1);
                     float f[N];
                     bool any = false;
 #pragma unroll
@@ -508,7 +507,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
                     mbar_wait(&ms.p_empty[sb], g / 2, abort_flag);
                     tc_fence_after();
-                    reduce_cols(l_acc, false);
+                    reduce_cols_128<N, false>(l_acc, ms.red, warp, lane, 1);
                     const bool whole = (t_begin <= wk.seq_t0) && (wk.seq_t1 <= t_end);
                     const int slot = w + wk.b;
                     float inv[N];

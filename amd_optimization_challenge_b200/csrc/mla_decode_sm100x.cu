@@ -53,9 +53,20 @@ struct Cfg {
     // with transform warps the gather role only moves Q and rope bytes; N = 32 runs 3 warps per scheduler either
     // way (registers are handed out per scheduler), so a hybrid cache's rope gather gets the two spare warps
     static constexpr int PW = XF ? 1 : (N == 16 ? 8 : 4);
-    static constexpr int XW = XF ? ((N == 16 || (ROPE_SEP && !QSPLIT)) ? 8 : 4) : 0;
+    static constexpr int XW = XF ? ((N != 64 && (N == 16 || (ROPE_SEP && !QSPLIT))) ? 8 : 4) : 0;
     static constexpr int PRODUCERS = 32 * PW, XT = 32 * XW;
-    static constexpr int THREADS = 160 + PRODUCERS + XT;
+    // N = 64: two softmax warpgroups of 128 threads, each with 32 of the 64 query rows (warps w and w + 4 reach the same
+    // TMEM lanes), so that a tile is gathered, converted and multiplied once for 64 rows with the softmax cost of 32.
+    static constexpr int SMG = N == 64 ? 2 : 1;                   // softmax warpgroups
+    static constexpr int NC = N / SMG;                            // query rows (S / O columns) per softmax thread
+    static constexpr int SW = 4 * SMG;                            // softmax warps; warp SW issues the MMAs
+    static constexpr int FIRST_PRODUCER = 32 * (SW + 1);
+    static constexpr int THREADS = FIRST_PRODUCER + PRODUCERS + XT;
+    // N = 64: P_hi and P_lo are two k-steps into the SAME O columns (O = 4 x N columns; with them side by side O alone
+    // would fill the 512 TMEM columns), P_lo is then stored unscaled, and P is single buffered (shared memory).
+    static constexpr bool MERGED = N == 64;
+    static constexpr int OB = MERGED ? N : 2 * N;                 // TMEM columns of one O block
+    static constexpr int P_BUFS = MERGED ? 1 : 2;
     static constexpr int NB = KVFMT == KV_MXFP4 ? 18 : 16;        // 32-code blocks per cache row
     static constexpr int RAW_ROW = NB * 16;                       // bytes of codes per row
     static constexpr int PITCH = RAW_ROW + 16;                    // row pitch in a landing buffer: eight rows hit eight bank groups
@@ -66,23 +77,24 @@ struct Cfg {
     static constexpr int P_CHUNKS = 2 * N / 16;
     static constexpr int P_BUF_BYTES = P_CHUNKS * TILE * 16;
     static constexpr int MISC_RESERVE = 4096;                     // Misc + the tile prefix of ~700 sequences
-    static constexpr int FIXED = NS * STAGE_BYTES + Q_BYTES + 2 * P_BUF_BYTES + MISC_RESERVE;
+    static constexpr int FIXED = NS * STAGE_BYTES + Q_BYTES + P_BUFS * P_BUF_BYTES + MISC_RESERVE;
     // Landing buffers of the transform warps: S per warp, private to it
     static constexpr int RB_FIT = XF ? (SMEM_LIMIT - FIXED) / UNIT_BYTES : 0;
     static constexpr int S = !XF ? 0 : (RB_FIT >= 2 * XW ? 2 : 1);
     static constexpr int RB = XW * S;
     static constexpr int OFF_Q = NS * STAGE_BYTES;
     static constexpr int OFF_P = OFF_Q + Q_BYTES;
-    static constexpr int OFF_RAW = OFF_P + 2 * P_BUF_BYTES;
+    static constexpr int OFF_RAW = OFF_P + P_BUFS * P_BUF_BYTES;
     static constexpr int OFF_MISC = OFF_RAW + RB * UNIT_BYTES;
     static constexpr int TMEM_O = 2 * SC;
-    static constexpr int TMEM_NEED = 2 * SC + 8 * N;
+    static constexpr int TMEM_NEED = 2 * SC + 4 * OB;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
     // rows of a stage handed back to the transform warps after each PV token step instead of after the whole PV:
     // worth 2-4 % for the pure MXFP4 cache; not for the hybrid one, whose rope gather waits for the whole stage anyway
     static constexpr bool ROWS_EARLY = XF && !ROPE_SEP;
     static constexpr int KV_FULL_COUNT = XF ? 32 * XW + (ROPE_SEP ? PRODUCERS : 0) : PRODUCERS;
     static_assert(TMEM_NEED <= 512, "TMEM columns");
+    static_assert(N != 64 || !QSPLIT, "64 rows per CTA: e4m3 Q only");
     static_assert(!XF || RB_FIT >= XW, "landing buffers");
     static_assert((UNIT_TOK * NB) % 32 == 0 && UNIT_BYTES % 16 == 0, "unit layout");
 };
@@ -96,7 +108,8 @@ struct Misc {
     unsigned int q_amax;         // block_q_scale's word
     int tile_exp[NS][TILE / UNIT_TOK];   // exponent frame of each 16-token unit of the tile in each operand stage
     int slot[NS][TILE];
-    float red[4][32];            // softmax cross-warp exchange
+    __align__(16) float red[2][4][32];   // softmax cross-warp exchange, per softmax warpgroup
+    float nm[2][2][32];          // P_SCALE_LOG2 - reference maximum per query row: [warpgroup][double buffer][row]
 };
 
 // 2^e as a float; 0 below the normal range
@@ -164,15 +177,15 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             for (int q = 0; q < 4; ++q) mbar_init(&ms.kv_rows_free[i][q], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128);
-            mbar_init(&ms.p_full[i], 128); mbar_init(&ms.p_empty[i], 1);
+            mbar_init(&ms.s_full[i], 1); mbar_init(&ms.s_empty[i], 128 * C::SMG);
+            mbar_init(&ms.p_full[i], 128 * C::SMG); mbar_init(&ms.p_empty[i], 1);
         }
         mbar_init(&ms.q_full, PRODUCERS); mbar_init(&ms.q_empty, 1);
-        mbar_init(&ms.o_free, 128);
+        mbar_init(&ms.o_free, 128 * C::SMG);
         ms.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) { tmem_alloc(&ms.tmem_base, C::TMEM_COLS); tmem_relinquish(); }
+    if (warp == C::SW) { tmem_alloc(&ms.tmem_base, C::TMEM_COLS); tmem_relinquish(); }
     build_tile_prefix(p.kv_indptr, p.batch, TILE, prefix);       // ends with __syncthreads()
     tc_fence_after();
     const uint32_t tmem = ms.tmem_base;
@@ -186,11 +199,12 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
     volatile int* abort_flag = &ms.abort_flag;
 
     if (n_total > 0) {
-        if (warp >= 5 && warp < 5 + C::PW) {
+        if (warp >= C::SW + 1 && warp < C::SW + 1 + C::PW) {
             // =========================== gather ===========================
-            const int pt = tid - 160;
+            const int pt = tid - C::FIRST_PRODUCER;
             Walker wk; wk.init(prefix, p.batch, t_begin);
             Walker wn = wk;                                       // one tile ahead, for the page-table prefetch
+            bool bad_page = false;
             constexpr int SLOTS_PER_THREAD = (TILE + PRODUCERS - 1) / PRODUCERS;
             int my_slot[SLOTS_PER_THREAD];
             auto slots_for = [&](int g) {
@@ -237,7 +251,11 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     named_bar_sync(2, PRODUCERS);
 #pragma unroll
                     for (int k = 0; k < SLOTS_PER_THREAD; ++k)
-                        if (pt + k * PRODUCERS < TILE) ms.slot[st][pt + k * PRODUCERS] = my_slot[k];
+                        if (pt + k * PRODUCERS < TILE) {
+                            ms.slot[st][pt + k * PRODUCERS] = my_slot[k];
+                            // reporting (see clamp_slot): looked at here, where the id has arrived anyway, never at its load
+                            bad_page |= my_slot[k] != -1 && (unsigned int)my_slot[k] > p.last_slot;      // -1: no row (past the end)
+                        }
                     named_bar_sync(2, PRODUCERS);
                     slots_for(g + 1);
                 }
@@ -312,11 +330,12 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 }
             }
             cp_async_wait_all();
-        } else if (warp == 4) {
+            if (bad_page) atomicOr(p.status, (int)ST_BAD_PAGE);
+        } else if (warp == C::SW) {
             // =========================== MMA issue (whole warp, one elected lane per instruction) ===========================
             {
                 constexpr uint32_t IDESC_QK = make_idesc(TILE, NQ, false, false);
-                constexpr uint32_t IDESC_PV = make_idesc(128, 2 * N, true, true);
+                constexpr uint32_t IDESC_PV = make_idesc(128, C::OB, true, true);
                 // descriptor bases; per-MMA descriptors differ only in the start address
                 const uint64_t d_qk_a = make_desc(smem_base, 16, 1024, SWIZZLE_128B);                              // + stage
                 const uint64_t d_qk_a_rope = make_desc(smem_base + 4 * PANEL_BYTES, 16, 512, SWIZZLE_64B);         // + stage
@@ -357,18 +376,24 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 };
                 // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
                 auto issue_pv = [&](int g, bool first) {
-                    const int st = g % NS, pb = g & 1;
+                    const int st = g % NS, pb = g % C::P_BUFS;
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
                     const uint64_t b0 = desc_advance(d_pv_b, pb * C::P_BUF_BYTES);
                     // token steps outside, dim blocks inside: after step kk nothing reads tokens 32kk..32kk+31 of the stage
-                    // any more, and (ROWS_EARLY) the transform warps of those rows may write the tile after next
+                    // any more, and (ROWS_EARLY) the transform warps of those rows may write the tile after next.
+                    // MERGED: the hi and the lo term of P are two k-steps into the same O columns (the lo chunks follow
+                    // the hi chunks in the P buffer); otherwise they are the two halves of the MMA's 2N columns.
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            umma_f8_elect(tmem + C::TMEM_O + j * 2 * N, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
-                                    desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
+                        for (int half = 0; half < (C::MERGED ? 2 : 1); ++half) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                umma_f8_elect(tmem + C::TMEM_O + j * C::OB, desc_advance(a0, j * PANEL_BYTES + kk * 32 * 128),
+                                              desc_advance(b0, kk * 32 * 16 + half * (N / 16) * TILE * 16), IDESC_PV,
+                                              (first && kk == 0 && half == 0) ? 0u : 1u);
+                            }
                         }
                         if (C::ROWS_EARLY) umma_commit_elect(&ms.kv_rows_free[st][kk]);
                     }
@@ -382,7 +407,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 long long t_idle = clock64();
                 uint32_t spins = 0;
                 while (nv < n_total) {
-                    bool pv_ready = nv < nq && mbar_try_nb(&ms.p_full[nv & 1], (uint32_t)(nv / 2) & 1u);
+                    bool pv_ready = nv < nq && mbar_try_nb(&ms.p_full[nv % C::P_BUFS], (uint32_t)(nv / C::P_BUFS) & 1u);
                     // the first PV of a sequence overwrites O: the previous sequence's epilogue must have read it
                     if (pv_ready && v_first && wv.pair > 0) pv_ready = mbar_try_nb(&ms.o_free, (uint32_t)(wv.pair - 1) & 1u);
                     bool qk_ready = !pv_ready && nq < n_total &&
@@ -417,7 +442,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     }
                 }
             }
-        } else if (C::XF && warp >= 5 + C::PW) {
+        } else if (C::XF && warp >= C::SW + 1 + C::PW) {
             // =========================== transform (block-scaled caches) ===========================
             // Warp xw owns the 16-token units xw, xw + XW, ... of every tile and S private landing buffers.  For each
             // unit it fetches the raw rows itself (16-byte cp.async of the codes, the aligned 8-byte words around the
@@ -430,7 +455,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             constexpr int UPW = (TILE / UNIT_TOK) / (C::XW > 0 ? C::XW : 1);   // units per warp per tile
             constexpr int S = C::S > 0 ? C::S : 1;
             constexpr int CODE_IT = UNIT_TOK * C::NB / 32, PER = CODE_IT + 2;   // copy instructions per lane per unit: codes, E8M0 words
-            const int xw = warp - 5 - C::PW;
+            const int xw = warp - C::SW - 1 - C::PW;
             const int tok = lane & (UNIT_TOK - 1), par = lane >> 4;
             const int J = n_total * UPW;                                  // units of this warp
             Walker wn; wn.init(prefix, p.batch, t_begin);
@@ -470,6 +495,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                                   (sl < 0 || wd >= nwords) ? 0u : 8u);
                 }
             };
+            bool bad_page = false;
             int held[S];                                                  // row slots of the units now in the buffers
             int nxt = fetch_slot(0);
 #pragma unroll
@@ -487,6 +513,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 __syncwarp();                                             // ... and every other lane's
                 const unsigned char* unit = smem + C::OFF_RAW + (xw * S + buf) * C::UNIT_BYTES;
                 const int cur = S == 1 ? held[0] : (buf == 0 ? held[0] : held[S - 1]);
+                // reporting (see clamp_slot): once per unit and row, on a value that has arrived anyway
+                bad_page |= cur != -1 && (unsigned int)cur > p.last_slot;                     // -1: no row (past the end)
                 // the unit moves into registers: blocks par, par + 2, ... of row tok with their E8M0 bytes (a zero-filled
                 // row reads as codes 0, scale 0)
                 const int o = (int)(reinterpret_cast<uintptr_t>(p.kv_bs + (long long)clamp_slot(p, cur) * p.kv_bs_stride) & 7);
@@ -508,13 +536,18 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 nxt = nxt2;
                 nxt2 = fetch_slot(j + S + 2);
                 const int e_unit = (int)__reduce_max_sync(0xffffffffu, e);
-                // The arithmetic needs no operand stage, so it is done (and pinned in registers) before the wait for the
-                // stage: only the stores are left on the path between "stage free" and "tile ready".
-                uint4 ob[2 * NBH];
+                // The arithmetic needs no operand stage.  With 16 query rows per CTA it is done (and pinned in registers) before
+                // the wait for the stage, so that only the stores are left between "stage free" and "tile ready"; for a hybrid
+                // cache with 32 rows and for 64 rows the 64 registers of the converted unit do not fit beside the softmax role's (the
+                // kernel spilled, and with nearly all of L1 configured as shared memory a spill is an L2 round trip): convert block by block.
+                constexpr bool PIN = N == 16 || (N == 32 && !C::ROPE_SEP);
+                uint4 ob[PIN ? 2 * NBH : 2];
+                if (PIN) {
 #pragma unroll
-                for (int i = 0; i < NBH; ++i) dequant_block(v[i], (int)sc[i] - e_unit + 6, ob[2 * i], ob[2 * i + 1]);
+                    for (int i = 0; i < NBH; ++i) dequant_block(v[i], (int)sc[i] - e_unit + 6, ob[PIN ? 2 * i : 0], ob[PIN ? 2 * i + 1 : 1]);
 #pragma unroll
-                for (int i = 0; i < 2 * NBH; ++i) asm volatile("" : "+r"(ob[i].x), "+r"(ob[i].y), "+r"(ob[i].z), "+r"(ob[i].w));
+                    for (int i = 0; i < (PIN ? 2 * NBH : 0); ++i) asm volatile("" : "+r"(ob[i].x), "+r"(ob[i].y), "+r"(ob[i].z), "+r"(ob[i].w));
+                }
                 // this unit's rows of the stage are free (the whole stage where the rows are not released one by one)
                 if (C::ROWS_EARLY) mbar_wait(&ms.kv_rows_free[st][k / 2], g / NS - 1, abort_flag);
                 else if (ku == 0) mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
@@ -524,8 +557,9 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
 #pragma unroll
                 for (int i = 0; i < NBH; ++i) {
                     unsigned char* d = (2 * (2 * i) >= 32 ? dst_rope : dst_lat) + st_off[i];   // block par + 2i >= 16: rope dims
-                    *reinterpret_cast<uint4*>(d) = ob[2 * i];
-                    *reinterpret_cast<uint4*>(reinterpret_cast<uintptr_t>(d) ^ 16) = ob[2 * i + 1];
+                    if (!PIN) dequant_block(v[i], (int)sc[i] - e_unit + 6, ob[0], ob[1]);
+                    *reinterpret_cast<uint4*>(d) = ob[PIN ? 2 * i : 0];
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uintptr_t>(d) ^ 16) = ob[PIN ? 2 * i + 1 : 1];
                 }
                 if (ku == UPW - 1) {
                     fence_proxy_async();                                  // the MMA reads the tile through the async proxy
@@ -533,39 +567,28 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 }
             }
             cp_async_wait_all();
-        } else if (warp < 4) {
-            // =========================== softmax / correction / epilogue (128 threads) ===========
-            const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-            // idle until the first scores exist: look over the page ids of this CTA's span (reporting only, see clamp_slot)
-            if (blockIdx.y == 0) check_span_pages(p, prefix, t_begin, t_end, TILE, tid, 128);
+            if (bad_page && blockIdx.y == 0) atomicOr(p.status, (int)ST_BAD_PAGE);
+        } else if (warp < C::SW) {
+            // =========================== softmax / correction / epilogue (128 threads per warpgroup) ===========
+            // warpgroup sg owns the query rows (S / O columns) [col0, col0 + NC); thread = token `tok` = TMEM lane
+            constexpr int NC = C::NC;
+            const int sg = warp >> 2, tok = tid & 127, col0 = sg * NC, bar_id = 1 + 2 * sg;
+            const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
             Walker wk; wk.init(prefix, p.batch, t_begin);
             float qk_base = 0.0f;          // sm_scale * log2(e) * (scale of this sequence's Q bytes)
             int e_run = 0;                 // exponent frame of O (block-scaled caches)
-            // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key
-            float nm[N], l_acc[N];
+            // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key.  The same
+            // value in all 128 threads, so it lives in shared memory (read as a broadcast) rather than in NC registers per
+            // thread; it changes only on the re-centering path, which writes the other half of a double buffer, then syncs.
+            // (Only where the registers are needed - hybrid caches and 64 rows per CTA, whose kernels spilled otherwise; the
+            // other variants keep the array in registers, which is 6 % faster on the long-context MXFP4 shape.)
+            constexpr bool NM_SMEM = C::ROPE_SEP || N == 64;
+            float l_acc[NC], nm_r[NM_SMEM ? 1 : NC];
+            int nm_cur = 0;
+            auto nm = [&](int c) -> float { return NM_SMEM ? ms.nm[sg][nm_cur][c] : nm_r[NM_SMEM ? 0 : c]; };
             // token position pos is visible to the rows of 16-column chunk q iff pos < lim[q]
             // (heads is a multiple of 16, so the query index j is constant inside a chunk)
-            int lim[N / 16], lim_min = 0;
-            // per-column reduction over the 128 threads; result replicated in every thread
-            auto reduce_cols = [&](float (&v)[N], bool is_max) {
-#pragma unroll
-                for (int c = 0; c < N; ++c) {
-                    float x = v[c];
-#pragma unroll
-                    for (int o = 16; o >= 1; o >>= 1) {
-                        const float y = __shfl_xor_sync(0xffffffffu, x, o);
-                        x = is_max ? fmaxf(x, y) : x + y;
-                    }
-                    if (lane == 0) ms.red[warp][c] = x;
-                }
-                named_bar_sync(1, 128);
-#pragma unroll
-                for (int c = 0; c < N; ++c) {
-                    const float a0 = ms.red[0][c], a1 = ms.red[1][c], a2 = ms.red[2][c], a3 = ms.red[3][c];
-                    v[c] = is_max ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : (a0 + a1) + (a2 + a3);
-                }
-                named_bar_sync(1, 128);
-            };
+            int lim[NC / 16], lim_min = 0;
             for (int g = 0; g < n_total; ++g) {
                 const int sb = g & 1, st = g % NS;
                 const bool first = wk.seek(p, prefix, t_begin + g);
@@ -573,11 +596,19 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 const int pos_first = (t_begin + g - wk.seq_t0) * TILE;
                 if (first) {
 #pragma unroll
-                    for (int c = 0; c < N; ++c) { nm[c] = INFINITY; l_acc[c] = 0.0f; }
+                    for (int c = 0; c < NC; ++c) l_acc[c] = 0.0f;
+                    if (NM_SMEM) {
+                        named_bar_sync(bar_id, 128);              // every thread has read the previous sequence's maxima
+                        if (tok < NC) ms.nm[sg][nm_cur][tok] = INFINITY;
+                        named_bar_sync(bar_id, 128);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) nm_r[NM_SMEM ? 0 : c] = INFINITY;
+                    }
                     lim_min = 0x7fffffff;
 #pragma unroll
-                    for (int q = 0; q < N / 16; ++q) {
-                        const int j = (row0 + 16 * q) / p.heads;
+                    for (int q = 0; q < NC / 16; ++q) {
+                        const int j = (row0 + col0 + 16 * q) / p.heads;
                         const int causal_lim = p.causal ? (wk.tot_len - p.q_len + j + 1 - wk.pos_off) : 0x7fffffff;
                         lim[q] = min(wk.seq_len, causal_lim);
                         lim_min = min(lim_min, lim[q]);
@@ -591,7 +622,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 int e_unit = 0, e_tile = 0;
                 if (C::XF) {
                     const volatile int* te = ms.tile_exp[st];
-                    e_unit = te[tid / UNIT_TOK];
+                    e_unit = te[tok / UNIT_TOK];
 #pragma unroll
                     for (int i = 0; i < TILE / UNIT_TOK; ++i) e_tile = max(e_tile, te[i]);
                 }
@@ -600,15 +631,15 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 // score of (this thread's token, query row c) in log2 units, read from the S accumulators.  The scores are not
                 // kept in registers beyond x: the rare re-centering path reads them again (the S buffer is handed back after it).
                 const uint32_t s_addr = tmem + lane_base + sb * C::SC;
-                auto load_scores = [&](float (&dst)[N]) {
+                auto load_scores = [&](float (&dst)[NC]) {
 #pragma unroll
-                    for (int c0 = 0; c0 < N; c0 += 16) {
+                    for (int c0 = 0; c0 < NC; c0 += 16) {
                         float v[16], vl[16], r[16], rl[16];
-                        tmem_ld16(s_addr + c0, v);
-                        if (C::QSPLIT) tmem_ld16(s_addr + N + c0, vl);
+                        tmem_ld16(s_addr + col0 + c0, v);
+                        if (C::QSPLIT) tmem_ld16(s_addr + N + col0 + c0, vl);
                         if (C::ROPE_SEP) {
-                            tmem_ld16(s_addr + NQ + c0, r);
-                            if (C::QSPLIT) tmem_ld16(s_addr + NQ + N + c0, rl);
+                            tmem_ld16(s_addr + NQ + col0 + c0, r);
+                            if (C::QSPLIT) tmem_ld16(s_addr + NQ + N + col0 + c0, rl);
                         }
                         tmem_wait_ld();
 #pragma unroll
@@ -622,20 +653,20 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 };
 
                 // x = log2-domain exponent of the stored probability: score - m_ref + P_SCALE_LOG2
-                const int pos = pos_first + tid;
+                const int pos = pos_first + tok;
                 const bool masked_tile = pos_first + TILE > lim_min;                 // uniform
-                float x[N];
+                float x[NC];
                 load_scores(x);
 #pragma unroll
-                for (int c = 0; c < N; ++c) x[c] += nm[c];
+                for (int c = 0; c < NC; ++c) x[c] += nm(c);
                 if (masked_tile) {
 #pragma unroll
-                    for (int c = 0; c < N; ++c) if (pos >= lim[c / 16]) x[c] = -INFINITY;
+                    for (int c = 0; c < NC; ++c) if (pos >= lim[c / 16]) x[c] = -INFINITY;
                 }
                 float xm = x[0];
 #pragma unroll
-                for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
-                const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
+                for (int c = 1; c < NC; ++c) xm = fmaxf(xm, x[c]);
+                const bool recenter = named_bar_or(bar_id, 128, xm > P_SCALE_LOG2 + RECENTER);
                 // a larger exponent frame than the one O is held in: O moves to the new frame
                 float o_frame = 1.0f;
                 if (C::XF) {
@@ -643,42 +674,51 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     if (e_tile > e_run) { o_frame = pow2i(e_run - e_tile); e_run = e_tile; }
                 }
                 if (recenter || o_frame != 1.0f) {
-                    float f[N];
+                    float f[NC];
                     bool any = o_frame != 1.0f;
 #pragma unroll
-                    for (int c = 0; c < N; ++c) f[c] = 1.0f;
+                    for (int c = 0; c < NC; ++c) f[c] = 1.0f;
                     if (recenter) {
-                        float sv[N], mx[N];
+                        float sv[NC], mx[NC];
                         load_scores(sv);
 #pragma unroll
-                        for (int c = 0; c < N; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : sv[c];
-                        reduce_cols(mx, true);
+                        for (int c = 0; c < NC; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : sv[c];
+                        reduce_cols_128<NC, true>(mx, ms.red[sg], warp & 3, lane, bar_id);
 #pragma unroll
-                        for (int c = 0; c < N; ++c) {
-                            const float m_old = P_SCALE_LOG2 - nm[c];                 // -inf for a fresh column
+                        for (int c = 0; c < NC; ++c) {
+                            const float m_old = P_SCALE_LOG2 - nm(c);                 // -inf for a fresh column
                             const float m_new = fmaxf(m_old, mx[c]);
                             f[c] = (m_new == m_old) ? 1.0f : (m_old == -INFINITY ? 0.0f : ex2(m_old - m_new));
                             any |= f[c] != 1.0f;
-                            nm[c] = P_SCALE_LOG2 - m_new;
+                            const float nm_new = P_SCALE_LOG2 - m_new;
+                            if (NM_SMEM) { if (tok == c) ms.nm[sg][nm_cur ^ 1][c] = nm_new; }
+                            else nm_r[NM_SMEM ? 0 : c] = nm_new;
                             l_acc[c] *= f[c];
-                            x[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : sv[c] + nm[c];
+                            x[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : sv[c] + nm_new;
+                        }
+                        if (NM_SMEM) {
+                            nm_cur ^= 1;
+                            named_bar_sync(bar_id, 128);          // the new maxima are in place for every thread
                         }
                     }
                     if (!first && any) {
                         // O holds the sequence's earlier tiles once PV(g-1) has completed; nothing else touches it until P(g) is published
-                        mbar_wait(&ms.p_empty[(g - 1) & 1], (g - 1) / 2, abort_flag);
+                        mbar_wait(&ms.p_empty[(g - 1) % C::P_BUFS], (g - 1) / C::P_BUFS, abort_flag);
                         tc_fence_after();
 #pragma unroll
                         for (int jb = 0; jb < 4; ++jb) {
 #pragma unroll
-                            for (int c0 = 0; c0 < 2 * N; c0 += 16) {
-                                float o[16];
-                                const uint32_t addr = tmem + lane_base + C::TMEM_O + jb * 2 * N + c0;
-                                tmem_ld16(addr, o);
-                                tmem_wait_ld();
+                            for (int h = 0; h < (C::MERGED ? 1 : 2); ++h) {      // side by side: the hi and the lo columns
 #pragma unroll
-                                for (int c = 0; c < 16; ++c) o[c] *= f[(c0 + c) % N] * o_frame;
-                                tmem_st16(addr, o);
+                                for (int c0 = 0; c0 < NC; c0 += 16) {
+                                    float o[16];
+                                    const uint32_t addr = tmem + lane_base + C::TMEM_O + jb * C::OB + h * N + col0 + c0;
+                                    tmem_ld16(addr, o);
+                                    tmem_wait_ld();
+#pragma unroll
+                                    for (int c = 0; c < 16; ++c) o[c] *= f[c0 + c] * o_frame;
+                                    tmem_st16(addr, o);
+                                }
                             }
                         }
                         tmem_wait_st();
@@ -689,11 +729,14 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 mbar_arrive(&ms.s_empty[sb]);                     // the scores have been read for the last time
                 // stored probability = p * 2^4 * 2^(e_unit - e_run): this token's V bytes are in the frame e_unit, O in e_run
                 const float p_frame = C::XF ? pow2i(e_unit - e_run) : 1.0f;
-                // P(g) may overwrite its buffer once PV(g-2) has completed
-                mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
-                uint8_t* pbuf = smem + C::OFF_P + sb * C::P_BUF_BYTES;
+                // P(g) may overwrite its buffer once the PV that read it last (tile g - P_BUFS) has completed
+                const int pb = g % C::P_BUFS;
+                mbar_wait(&ms.p_empty[pb], g / C::P_BUFS - 1, abort_flag);
+                uint8_t* pbuf = smem + C::OFF_P + pb * C::P_BUF_BYTES;
+                // MERGED: the lo term shares O's columns with the hi term, so it carries no factor of its own
+                constexpr float LO_GAIN = C::MERGED ? 1.0f : 16.0f;
 #pragma unroll
-                for (int c0 = 0; c0 < N; c0 += 16) {
+                for (int c0 = 0; c0 < NC; c0 += 16) {
                     uint32_t hi[4], lo[4];
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
@@ -707,42 +750,42 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                         }
                         hi[q4] = pack_e4m3x4(pv[0], pv[1], pv[2], pv[3]);
                         const float2 h01 = unpack_e4m3x2((uint16_t)(hi[q4] & 0xffffu)), h23 = unpack_e4m3x2((uint16_t)(hi[q4] >> 16));
-                        lo[q4] = pack_e4m3x4((pv[0] - h01.x) * 16.0f, (pv[1] - h01.y) * 16.0f,
-                                             (pv[2] - h23.x) * 16.0f, (pv[3] - h23.y) * 16.0f);
+                        lo[q4] = pack_e4m3x4((pv[0] - h01.x) * LO_GAIN, (pv[1] - h01.y) * LO_GAIN,
+                                             (pv[2] - h23.x) * LO_GAIN, (pv[3] - h23.y) * LO_GAIN);
                     }
-                    *reinterpret_cast<uint4*>(pbuf + (c0 / 16) * (TILE * 16) + tid * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (TILE * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4*>(pbuf + ((col0 + c0) / 16) * (TILE * 16) + tok * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4*>(pbuf + ((N + col0 + c0) / 16) * (TILE * 16) + tok * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
                 fence_proxy_async();
-                mbar_arrive(&ms.p_full[sb]);
+                mbar_arrive(&ms.p_full[pb]);
 
                 if (last) {
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
-                    mbar_wait(&ms.p_empty[sb], g / 2, abort_flag);
+                    mbar_wait(&ms.p_empty[pb], g / C::P_BUFS, abort_flag);
                     tc_fence_after();
-                    reduce_cols(l_acc, false);
+                    reduce_cols_128<NC, false>(l_acc, ms.red[sg], warp & 3, lane, bar_id);
                     const bool whole = (t_begin <= wk.seq_t0) && (wk.seq_t1 <= t_end);
                     const int slot = w + wk.b;
                     const float out_scale = C::XF ? pow2i(e_run - E_BIAS) : kv_tensor_scale;
-                    float inv[N];
+                    float inv[NC];
 #pragma unroll
-                    for (int c = 0; c < N; ++c) inv[c] = l_acc[c] > 0.0f ? __fdividef(out_scale, l_acc[c]) : 0.0f;
-                    // one output element per (row, dim): this thread owns dims tid, 128+tid, ... of every row
-                    const long long orow0 = whole ? ((long long)wk.b * p.rows + row0) : ((long long)slot * p.rows + row0);
+                    for (int c = 0; c < NC; ++c) inv[c] = l_acc[c] > 0.0f ? __fdividef(out_scale, l_acc[c]) : 0.0f;
+                    // one output element per (row, dim): this thread owns dims tok, 128 + tok, ... of its warpgroup's rows
+                    const long long orow0 = (whole ? (long long)wk.b * p.rows : (long long)slot * p.rows) + row0 + col0;
                     float* dst_f32 = whole ? p.out_o_f32 : p.part_o;
                     __nv_bfloat16* dst_bf16 = whole ? p.out : nullptr;
-                    if (dst_f32) dst_f32 += orow0 * V_DIM + tid;
-                    if (dst_bf16) dst_bf16 += orow0 * V_DIM + tid;
+                    if (dst_f32) dst_f32 += orow0 * V_DIM + tok;
+                    if (dst_bf16) dst_bf16 += orow0 * V_DIM + tok;
 #pragma unroll
                     for (int jb = 0; jb < 4; ++jb) {
 #pragma unroll
-                        for (int c0 = 0; c0 < N; c0 += 16) {
+                        for (int c0 = 0; c0 < NC; c0 += 16) {
                             float ohi[16], olo[16];
-                            tmem_ld16(tmem + lane_base + C::TMEM_O + jb * 2 * N + c0, ohi);
-                            tmem_ld16(tmem + lane_base + C::TMEM_O + jb * 2 * N + N + c0, olo);
+                            tmem_ld16(tmem + lane_base + C::TMEM_O + jb * C::OB + col0 + c0, ohi);
+                            if (!C::MERGED) tmem_ld16(tmem + lane_base + C::TMEM_O + jb * C::OB + N + c0, olo);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int c = 0; c < 16; ++c) ohi[c] = fmaf(olo[c], 0.0625f, ohi[c]) * inv[c0 + c];
+                            for (int c = 0; c < 16; ++c) ohi[c] = (C::MERGED ? ohi[c] : fmaf(olo[c], 0.0625f, ohi[c])) * inv[c0 + c];
                             if (dst_bf16) {
 #pragma unroll
                                 for (int c = 0; c < 16; ++c) dst_bf16[(c0 + c) * V_DIM + jb * 128] = __float2bfloat16_rn(ohi[c]);
@@ -756,13 +799,13 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     // O has been read: the next sequence's first PV may overwrite it
                     tc_fence_before();
                     mbar_arrive(&ms.o_free);
-                    if (tid < N) {
+                    if (tok < NC) {
                         float lsum = 0.0f, nmc = 0.0f;
 #pragma unroll
-                        for (int c = 0; c < N; ++c) if (c == tid) { lsum = l_acc[c]; nmc = nm[c]; }
+                        for (int c = 0; c < NC; ++c) if (c == tok) { lsum = l_acc[c]; nmc = nm(c); }
                         const float lse = lsum > 0.0f ? (log2f(lsum) - nmc) * LN2 : -INFINITY;
-                        if (whole) { if (p.out_lse) p.out_lse[(long long)wk.b * p.rows + row0 + tid] = lse; }
-                        else p.part_lse[(long long)slot * p.rows + row0 + tid] = lse;
+                        if (whole) { if (p.out_lse) p.out_lse[(long long)wk.b * p.rows + row0 + col0 + tok] = lse; }
+                        else p.part_lse[(long long)slot * p.rows + row0 + col0 + tok] = lse;
                     }
                 }
             }
@@ -771,7 +814,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
 
     __syncthreads();
     if (tid == 0 && ms.abort_flag) atomicOr(status, (int)ST_TIMEOUT);
-    if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+    if (warp == C::SW) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
 }
 
 // bf16 Q -> two e4m3 planes.  Block (group, sequence) takes the N query rows [group*N, group*N + N) of one
@@ -870,6 +913,12 @@ cudaError_t launch_cfg(const MlaParams& p, int* status, cudaStream_t stream, boo
 
 template <int N>
 cudaError_t dispatch_formats(const MlaParams& p, int* status, cudaStream_t stream, bool dry_run, bool* fits) {
+    if constexpr (N == 64) {                                      // 64 rows per CTA: e4m3 Q over a block-scaled cache
+        if (p.q_format == Q_E4M3 && p.kv_format == KV_MXFP4) return launch_cfg<64, KV_MXFP4, Q_E4M3>(p, status, stream, dry_run, fits);
+        if (p.q_format == Q_E4M3 && p.kv_format == KV_HYBRID) return launch_cfg<64, KV_HYBRID, Q_E4M3>(p, status, stream, dry_run, fits);
+        if (fits) *fits = false;
+        return cudaErrorInvalidValue;
+    } else {
     if (p.q_format == Q_BF16) {
         if (p.kv_format == KV_E4M3) return launch_cfg<N, KV_E4M3, Q_BF16>(p, status, stream, dry_run, fits);
         if (p.kv_format == KV_MXFP4) return launch_cfg<N, KV_MXFP4, Q_BF16>(p, status, stream, dry_run, fits);
@@ -879,11 +928,17 @@ cudaError_t dispatch_formats(const MlaParams& p, int* status, cudaStream_t strea
     if (p.kv_format == KV_HYBRID) return launch_cfg<N, KV_HYBRID, Q_E4M3>(p, status, stream, dry_run, fits);
     if (fits) *fits = false;                                      // e4m3 x e4m3 belongs to the plain tcgen05 kernel
     return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace
 
-int sm100x_rows_per_cta(const MlaParams& p) { return p.rows % 32 == 0 ? 32 : 16; }
+// 64 query rows per CTA where the format pair has that variant (a tile is then gathered and converted once per 64
+// rows), else 32 or 16.
+int sm100x_rows_per_cta(const MlaParams& p) {
+    if (p.rows % 64 == 0 && p.q_format == Q_E4M3 && p.kv_format != KV_E4M3) return 64;
+    return p.rows % 32 == 0 ? 32 : 16;
+}
 
 // Every format pair except e4m3 Q x e4m3 cache; the tile-prefix table must fit beside the rings.
 bool sm100x_supported(const MlaParams& p) {
@@ -891,7 +946,9 @@ bool sm100x_supported(const MlaParams& p) {
     // the E8M0 rows are fetched as three aligned 8-byte words: they must start on an even address
     if (p.kv_format != KV_E4M3 && ((reinterpret_cast<uintptr_t>(p.kv_bs) | (uintptr_t)p.kv_bs_stride) & 1u)) return false;
     bool fits = false;
-    if (sm100x_rows_per_cta(p) == 32) dispatch_formats<32>(p, nullptr, nullptr, true, &fits);
+    const int n = sm100x_rows_per_cta(p);
+    if (n == 64) dispatch_formats<64>(p, nullptr, nullptr, true, &fits);
+    else if (n == 32) dispatch_formats<32>(p, nullptr, nullptr, true, &fits);
     else dispatch_formats<16>(p, nullptr, nullptr, true, &fits);
     return fits;
 }
@@ -901,6 +958,7 @@ long long sm100x_q_split_bytes(int batch, int rows) { return 2LL * batch * rows 
 long long sm100x_q_scale_bytes(int batch, int rows) { return (long long)batch * (rows / 16) * 4; }
 
 cudaError_t launch_sm100x(const MlaParams& p, int* status, cudaStream_t stream) {
+    if (p.rows_per_cta == 64) return dispatch_formats<64>(p, status, stream, false, nullptr);
     return p.rows_per_cta == 32 ? dispatch_formats<32>(p, status, stream, false, nullptr)
                                 : dispatch_formats<16>(p, status, stream, false, nullptr);
 }

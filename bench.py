@@ -74,6 +74,14 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
+def measured_peak_tflops():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 def make_lens(w, seed):
     if isinstance(w["kv_len"], tuple):
         g = torch.Generator().manual_seed(seed)
@@ -562,10 +570,22 @@ def main():
     k_us = statistics.mean(k_ms) * 1e3
     peak, peak_kind = measured_peak_gbs()
     achieved = abytes / (k_us * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if mode == "replica" else None, "traffic_unit": "bytes per launch (ncu dram read + write, separate capture)",
-                "kernel": "mla_decode stage 1", "kernel_us": k_us,
-                "algorithmic_bytes": abytes, "peak_source": f"of {peak_kind}"}
+    hbm = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+           "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if mode == "replica" else None,
+           "traffic_unit": "bytes per launch (ncu dram read + write, separate capture of this kernel; profiles/)",
+           "kernel": "mla_decode stage 1", "kernel_us": k_us,
+           "algorithmic_bytes": abytes, "peak_source": f"of {peak_kind}"}
+    if w["heads"] >= 128:
+        # the H = 128 shape is bound by the tensor pipe, not by HBM: report it against the dense e4m3 rate
+        # (twice the measured dense bf16 rate; both operands are e4m3) and keep the HBM view beside it
+        flops = 2.0 * w["q_len"] * w["heads"] * host["total_kv"] * (576 + 512)
+        tf_peak, tf_kind = measured_peak_tflops()
+        tf = flops / (k_us * 1e-6) / 1e12
+        roofline = {"bound": "tensor", "achieved": tf, "peak": 2.0 * tf_peak, "unit": "TFLOP/s", "frac": tf / (2.0 * tf_peak),
+                    "traffic": hbm["traffic"], "kernel": hbm["kernel"], "kernel_us": k_us, "algorithmic_flops": flops,
+                    "peak_source": f"2 x dense bf16 burst, of {tf_kind}", "hbm": hbm}
+    else:
+        roofline = hbm
 
     # ---- end to end: host buffers in, host buffer out, every step
     pin = lambda t: t.contiguous().pin_memory()

@@ -52,6 +52,32 @@ def test_shard_batch_matches_whole():
         assert torch.equal(o, whole[rows])
 
 
+def test_split_kv_shard_covers_every_key_once():
+    """The per-rank page-table slices of the cross-GPU split-KV mode: every key of every sequence lands on exactly
+    one rank, with the position offset and total length the causal mask needs; merged partials equal the whole."""
+    B, QL, S, world = 3, 2, 700, 4
+    data = inputs.generate_input(B, QL, S, seed=11, shuffle_pages=True, device="cpu", formats=("fp8",))
+    q, kvd, _, kvp, cfg = data
+    idx = cfg["kv_indices"]
+    seen = []
+    parts_o, parts_l = [], []
+    kf = mo.dequant_kv("fp8", kvd["fp8"])
+    for r in range(world):
+        local, ip, off, tot, n = D.split_kv_shard(idx, B, S, r, world)
+        a, b = D.kv_range_partition(S, world)[r]
+        assert n == b - a and ip.tolist() == [i * n for i in range(B + 1)]
+        assert off.tolist() == [a] * B and tot.tolist() == [S] * B and local.dtype == torch.int32
+        if n:
+            seen.append(local.view(B, n))
+        o, l = mo.mla_decode(q.float(), kf, ip.numpy(), local.numpy(), cfg["sm_scale"], q_len=QL,
+                             kv_pos_offset=off.tolist(), kv_total_len=tot.tolist())
+        parts_o.append(o); parts_l.append(l)
+    assert torch.equal(torch.cat(seen, dim=1).reshape(-1), idx)
+    merged, _ = mo.merge_partials(torch.stack(parts_o), torch.stack(parts_l))
+    whole, _ = mo.mla_decode(q.float(), kf, kvp.numpy(), idx.numpy(), cfg["sm_scale"], q_len=QL)
+    assert torch.allclose(merged, whole, atol=1e-5)
+
+
 def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     return port
