@@ -31,6 +31,9 @@
 //
 // Role in the reference: the split-KV stage-1 kernels (mixed-mla/submission.py:122-250,
 // mixed-mla/versions/hip_mxfp4_v5/submission.py:214-656).
+#include <cuda.h>
+#include <cstring>
+
 #include "sm100_ptx.cuh"
 
 namespace b200mla {
@@ -86,7 +89,8 @@ struct Misc {
 };
 
 template <int N>
-__global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel(const MlaParams p, int* status) {
+__global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel(const MlaParams p, int* status, const __grid_constant__ CUtensorMap tmap_lat,
+                                                                                 const __grid_constant__ CUtensorMap tmap_rope, const int use_tma) {
     using L = Layout<N>;
     constexpr int PRODUCERS = L::PRODUCERS, THREADS = L::THREADS;
     constexpr int TILE = L::TILE, NS = L::NS, PANEL_BYTES = L::PANEL_BYTES, STAGE_BYTES = L::STAGE_BYTES;
@@ -252,6 +256,25 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 if (paged) mbar_wait(&ms.slot_full[g % SLOT_RING], g / SLOT_RING, abort_flag);
                 mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
                 const uint32_t stage_addr = smem_base + st * STAGE_BYTES;
+                // Contiguous cache (no page table: token t of the batch lives in slot t) and a tile that lies wholly inside
+                // its sequence: the tile is five tiled TMA copies (four 128-byte-wide panels, 128B swizzle, and the 64-byte
+                // rope panel, 64B swizzle) issued by one thread and completed on the stage's mbarrier by byte count; the
+                // other gather threads only arrive.  A tile that reaches past the end of its sequence takes the copy loop
+                // below, which zero-fills the missing rows (TMA would bring whatever follows in memory, and zero
+                // probabilities do not neutralise non-finite bytes).
+                if (use_tma && pos0 + TILE <= wk.seq_len) {
+                    if (pt == 0) {
+                        mbar_arrive_expect_tx(&ms.kv_full[st], (uint32_t)STAGE_BYTES);
+                        const int row = wk.seq_base + pos0;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) tma_load_2d(stage_addr + j * PANEL_BYTES, &tmap_lat, 128 * j, row, &ms.kv_full[st]);
+                        tma_load_2d(stage_addr + 4 * PANEL_BYTES, &tmap_rope, 512, row, &ms.kv_full[st]);
+                    } else {
+                        mbar_arrive(&ms.kv_full[st]);
+                    }
+                    if (q_due >= 0 && (g >= q_due || g == n_total - 1)) flush_q();
+                    continue;
+                }
                 // Slots first, then the copies, for the whole tile at once: a shared-memory load that sits between copy
                 // instructions waits behind them in the load/store unit, and the copies after it wait for the load
                 // (measured in isolation: 4.1 TB/s with two batches per tile, 5.4 TB/s with one).
@@ -577,14 +600,49 @@ bool sm100_supported(const MlaParams& p) {
     return need <= (size_t)sm100::SMEM_LIMIT;
 }
 
+// Tensor map over the cache plane [num_slots rows x 576 bytes] with a box of `box_bytes` x `box_rows`; false if the
+// driver entry point is missing or refuses the arguments (the caller then keeps the copy loop).
+static bool make_cache_map(CUtensorMap* map, const MlaParams& p, int box_bytes, int box_rows, CUtensorMapSwizzle swizzle) {
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = nullptr;
+    static bool looked_up = false;
+    if (!looked_up) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            encode = (encode_fn)fn;
+        looked_up = true;
+    }
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)QK_DIM, (cuuint64_t)p.num_slots};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.kv_codes_stride};
+    const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(p.kv_codes), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int N>
 static cudaError_t launch_n(const MlaParams& p, int* status, cudaStream_t stream) {
     using L = sm100::Layout<N>;
     const size_t smem = smem_need<N>(p.batch);
     cudaError_t e = cudaFuncSetAttribute(sm100::mla_decode_sm100_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
+    // contiguous cache: tiled TMA for the tiles (this GPU's own cache plane only; no multi-CTA delivery of any kind)
+    CUtensorMap lat, rope;
+    memset(&lat, 0, sizeof(lat));
+    memset(&rope, 0, sizeof(rope));
+    int use_tma = 0;
+    if (p.kv_indices == nullptr && p.kv_codes_stride % 16 == 0 && p.kv_codes_stride >= QK_DIM && p.num_slots > 0 &&
+        p.num_slots < (1LL << 31))
+        use_tma = make_cache_map(&lat, p, 128, L::TILE, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                  make_cache_map(&rope, p, 64, L::TILE, CU_TENSOR_MAP_SWIZZLE_64B);
     dim3 grid(p.num_ctas, p.rows / N);
-    sm100::mla_decode_sm100_kernel<N><<<grid, L::THREADS, smem, stream>>>(p, status);
+    sm100::mla_decode_sm100_kernel<N><<<grid, L::THREADS, smem, stream>>>(p, status, lat, rope, use_tma);
     return cudaGetLastError();
 }
 

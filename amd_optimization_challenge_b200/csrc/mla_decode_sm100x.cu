@@ -583,7 +583,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             // (Only where the registers are needed - hybrid caches and 64 rows per CTA, whose kernels spilled otherwise; the
             // other variants keep the array in registers, which is 6 % faster on the long-context MXFP4 shape.)
             constexpr bool NM_SMEM = C::ROPE_SEP || N == 64;
-            float l_acc[NC], nm_r[NM_SMEM ? 1 : NC];
+            float l_acc[NC], nm_r[NM_SMEM ? 1 : NC] = {};
             int nm_cur = 0;
             auto nm = [&](int c) -> float { return NM_SMEM ? ms.nm[sg][nm_cur][c] : nm_r[NM_SMEM ? 0 : c]; };
             // token position pos is visible to the rows of 16-column chunk q iff pos < lim[q]
