@@ -10,17 +10,20 @@
 // split into two e4m3 terms (P = hi + lo/16, the two halves of the 2N columns) so that the
 // probabilities keep ~8 significant bits.
 //
-// The CTA walks its span of 128-token tiles as one continuous stream: the gather, the MMA issue and
-// the softmax each run their own loop over the tiles and meet only through mbarriers, also across
-// the boundary between two sequences (Q is double buffered; only the first PV of the next sequence
-// waits until the epilogue has read O out of TMEM).
+// The CTA walks its span of tiles (112 tokens at N = 16, three stages; 128 at N = 32, two stages) as one continuous
+// stream: the gather, the MMA issue and the softmax each run their own loop over the tiles and meet only through
+// mbarriers, also across the boundary between two sequences (Q is double buffered; only the first PV of the next
+// sequence waits until the epilogue has read O out of TMEM).
 //
 // Roles:  warps 0-3  softmax / correction / epilogue (one TMEM lane = one token / one output dim per thread)
-//         warp  4    tcgen05.mma issue (one lane, event driven), TMEM allocation
-//         warps 5..  paged gather: 16-byte cp.async of cache rows (and of Q) through the page table
-//                    straight into the 128B-swizzled UMMA layout, completion signalled on an mbarrier.
+//         warp  4    tcgen05.mma issue (the whole warp runs the loop, one elected lane issues), TMEM allocation
+//         warps 5..  gather of the cache rows (and of the Q rows of each sequence) straight into the swizzled UMMA
+//                    layout, completion signalled on the stage's mbarrier:
+//                      contiguous cache (no page table)  tiled TMA, five cp.async.bulk.tensor.2d copies per tile
+//                      page table                        16-byte cp.async per row piece; the page ids reach shared
+//                                                        memory by 4-byte cp.async three tiles ahead
 // Movers measured on B200 for shuffled 576-byte rows, device-wide, one CTA per SM:
-//         16-byte cp.async (LSU)                       3.5 - 4.4 TB/s, lands directly in operand layout
+//         16-byte cp.async, 6 / 9 / 11 / 16 / 24 warps 3.9 / 4.3 / 4.1 / 5.4 / 5.2 TB/s, lands directly in operand layout
 //         TMA tile::gather4 (4 rows x 128 B / instr)   1.3 - 2.9 TB/s, ~60 cycles per instruction
 //         one cp.async.bulk per row, 4 issuing warps   5.3 TB/s, but row-major: needs ~80 KB of raw staging
 //                                                      per SM beside the operand tiles plus a re-layout pass
@@ -633,14 +636,30 @@ static cudaError_t launch_n(const MlaParams& p, int* status, cudaStream_t stream
     cudaError_t e = cudaFuncSetAttribute(sm100::mla_decode_sm100_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     // contiguous cache: tiled TMA for the tiles (this GPU's own cache plane only; no multi-CTA delivery of any kind)
+    // The maps depend on the plane's address, row count and stride only; the last few are kept per host thread, so a
+    // serving loop that decodes from the same cache does not pay the two driver calls (~3 us) on every call.
+    struct MapEntry { const void* base; long long slots, stride; int tile, ok; CUtensorMap lat, rope; };
+    static thread_local MapEntry cache[4] = {};
+    static thread_local int next = 0;
     CUtensorMap lat, rope;
     memset(&lat, 0, sizeof(lat));
     memset(&rope, 0, sizeof(rope));
     int use_tma = 0;
     if (p.kv_indices == nullptr && p.kv_codes_stride % 16 == 0 && p.kv_codes_stride >= QK_DIM && p.num_slots > 0 &&
-        p.num_slots < (1LL << 31))
-        use_tma = make_cache_map(&lat, p, 128, L::TILE, CU_TENSOR_MAP_SWIZZLE_128B) &&
-                  make_cache_map(&rope, p, 64, L::TILE, CU_TENSOR_MAP_SWIZZLE_64B);
+        p.num_slots < (1LL << 31)) {
+        MapEntry* hit = nullptr;
+        for (MapEntry& m : cache)
+            if (m.base == p.kv_codes && m.slots == p.num_slots && m.stride == p.kv_codes_stride && m.tile == L::TILE) hit = &m;
+        if (!hit) {
+            hit = &cache[next];
+            next = (next + 1) % 4;
+            hit->base = p.kv_codes; hit->slots = p.num_slots; hit->stride = p.kv_codes_stride; hit->tile = L::TILE;
+            hit->ok = make_cache_map(&hit->lat, p, 128, L::TILE, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                      make_cache_map(&hit->rope, p, 64, L::TILE, CU_TENSOR_MAP_SWIZZLE_64B);
+        }
+        use_tma = hit->ok;
+        if (use_tma) { lat = hit->lat; rope = hit->rope; }
+    }
     dim3 grid(p.num_ctas, p.rows / N);
     sm100::mla_decode_sm100_kernel<N><<<grid, L::THREADS, smem, stream>>>(p, status, lat, rope, use_tma);
     return cudaGetLastError();

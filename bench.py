@@ -53,9 +53,9 @@ KV_ROW_BYTES = {"fp8": 576, "mxfp4": 306, "hybrid": 336}
 # how a workload uses N > 1 GPUs: independent replicas (weak scaling), a token-balanced split of the
 # batch (strong, no collective), or each sequence's keys split over the GPUs (strong, one all-gather)
 MODES = {"c1": "replica", "c2": "replica", "c3": "batch_shard", "c4": "split_kv"}
-# DRAM bytes read + written by one stage-1 launch, from one ncu capture of that workload on one GPU
-# (profiles/ holds the capture's summary and command); None where no capture was taken.
-NCU_TRAFFIC_BYTES = {"c1": 78.8e6, "c2": 191.9e6, "c3": 742.4e6, "c4": 427.7e6}
+# DRAM bytes read + written by one stage-1 launch, from one ncu capture of that workload's kernel on one GPU
+# (profiles/ holds each capture's summary and command; regenerate them together with the kernels).
+NCU_TRAFFIC_BYTES = {"c1": 83.3e6, "c2": 190.0e6, "c3": 770.0e6, "c4": 428.0e6}
 L2_BYTES = 126 << 20
 
 
