@@ -46,9 +46,21 @@ class KvAppendArgs(ctypes.Structure):
     ]
 
 
+class PeerMergeArgs(ctypes.Structure):
+    """struct b200_mla_peer_merge_args"""
+    _fields_ = [
+        ("world", _i32), ("rank", _i32), ("epoch", ctypes.c_uint32), ("wait_limit_ms", ctypes.c_uint32),
+        ("bases", ctypes.POINTER(_vp)), ("rows", _i64), ("out", _vp), ("workspace", _vp),
+    ]
+
+
+PEER_HANDLE_BYTES = 64
+
 EXPORTS = ("b200_mla_version", "b200_mla_last_error", "b200_mla_workspace_bytes", "b200_mla_decode",
            "b200_mla_combine", "b200_mla_quantize_fp8", "b200_mla_q_amax", "b200_mla_set_stage1_events",
-           "b200_mla_decode_static", "b200_mla_read_status", "b200_mla_reset_status", "b200_mla_kv_append")
+           "b200_mla_decode_static", "b200_mla_read_status", "b200_mla_reset_status", "b200_mla_kv_append",
+           "b200_mla_peer_exchange_bytes", "b200_mla_peer_partial_offset", "b200_mla_peer_alloc", "b200_mla_peer_open",
+           "b200_mla_peer_close", "b200_mla_peer_free", "b200_mla_peer_merge")
 STATUS_TIMEOUT, STATUS_BAD_PAGE = 1, 2
 
 
@@ -78,6 +90,20 @@ def _load() -> ctypes.CDLL:
     lib.b200_mla_reset_status.argtypes = [_vp, _vp]
     lib.b200_mla_kv_append.restype = _i32
     lib.b200_mla_kv_append.argtypes = [ctypes.POINTER(KvAppendArgs), _vp]
+    lib.b200_mla_peer_exchange_bytes.restype = _i64
+    lib.b200_mla_peer_exchange_bytes.argtypes = [_i64]
+    lib.b200_mla_peer_partial_offset.restype = _i64
+    lib.b200_mla_peer_partial_offset.argtypes = [_i64, ctypes.c_uint32]
+    lib.b200_mla_peer_alloc.restype = _i32
+    lib.b200_mla_peer_alloc.argtypes = [_i64, ctypes.POINTER(_vp), ctypes.c_char_p]
+    lib.b200_mla_peer_open.restype = _i32
+    lib.b200_mla_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(_vp)]
+    lib.b200_mla_peer_close.restype = _i32
+    lib.b200_mla_peer_close.argtypes = [_vp]
+    lib.b200_mla_peer_free.restype = _i32
+    lib.b200_mla_peer_free.argtypes = [_vp]
+    lib.b200_mla_peer_merge.restype = _i32
+    lib.b200_mla_peer_merge.argtypes = [ctypes.POINTER(PeerMergeArgs), _vp]
     lib.b200_mla_set_stage1_events.restype = _i32
     lib.b200_mla_set_stage1_events.argtypes = [_vp, _vp]
     return lib

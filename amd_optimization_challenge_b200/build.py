@@ -15,7 +15,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libb200mla.so")
-SOURCES = ["cabi.cu", "mla_decode_generic.cu", "mla_decode_sm100.cu", "mla_decode_sm100x.cu", "mla_combine.cu", "q_quant.cu", "kv_append.cu"]
+SOURCES = ["cabi.cu", "mla_decode_generic.cu", "mla_decode_sm100.cu", "mla_decode_sm100x.cu", "mla_combine.cu", "q_quant.cu", "kv_append.cu", "peer_merge.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -29,6 +29,11 @@ cudaError_t launch_kv_append(const void* src, long long n, long long src_stride,
                              long long num_slots, int kv_format, void* codes, long long codes_stride, void* bs,
                              long long bs_stride, void* rope, long long rope_stride, const float* scale, int* bad,
                              cudaStream_t stream);
+long long peer_part_bytes(long long rows);
+long long peer_exchange_bytes(long long rows);
+long long peer_partial_offset(long long rows, unsigned int epoch);
+cudaError_t launch_peer_merge(const void* const* bases, int world, int rank, unsigned int epoch, unsigned long long limit_ns,
+                              long long rows, void* out, int* status, cudaStream_t stream);
 cudaError_t launch_q_amax_parts(const __nv_bfloat16* x, long long n, unsigned int* parts, cudaStream_t stream);
 }  // namespace b200mla
 
@@ -280,6 +285,80 @@ int32_t b200_mla_combine(const float* o_parts, const float* lse_parts, int32_t p
     cudaError_t e = launch_combine_parts(o_parts, lse_parts, parts, rows, o_part_stride, lse_part_stride,
                                         (__nv_bfloat16*)out, out_lse, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+int64_t b200_mla_peer_exchange_bytes(int64_t rows) { return rows > 0 ? peer_exchange_bytes(rows) : 0; }
+
+int64_t b200_mla_peer_partial_offset(int64_t rows, uint32_t epoch) { return rows > 0 ? peer_partial_offset(rows, epoch) : 0; }
+
+int32_t b200_mla_peer_alloc(int64_t rows, void** base, unsigned char* handle) {
+    if (!base || !handle) return fail(B200_MLA_ERR_INVALID_ARG, "base and handle are required");
+    if (rows <= 0) return fail(B200_MLA_ERR_INVALID_ARG, "rows must be positive");
+    static_assert(sizeof(cudaIpcMemHandle_t) == B200_MLA_PEER_HANDLE_BYTES, "handle size");
+    void* ptr = nullptr;
+    const size_t bytes = (size_t)peer_exchange_bytes(rows);
+    cudaError_t e = cudaMalloc(&ptr, bytes);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "exchange allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    e = cudaMemset(ptr, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ptr);
+    if (e != cudaSuccess) {
+        cudaFree(ptr);
+        return fail(B200_MLA_ERR_CUDA, "exchange allocation cannot be exported: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle, &h, sizeof(h));
+    *base = ptr;
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_peer_open(const unsigned char* handle, void** base) {
+    if (!base || !handle) return fail(B200_MLA_ERR_INVALID_ARG, "base and handle are required");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* ptr = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200_MLA_ERR_CUDA, "peer allocation cannot be mapped: %s", cudaGetErrorString(e));
+    }
+    *base = ptr;
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_peer_close(void* base) {
+    if (!base) return B200_MLA_OK;
+    cudaError_t e = cudaIpcCloseMemHandle(base);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "peer mapping cannot be closed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_peer_free(void* base) {
+    if (!base) return B200_MLA_OK;
+    cudaError_t e = cudaFree(base);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "exchange allocation cannot be freed: %s", cudaGetErrorString(e));
+    return B200_MLA_OK;
+}
+
+int32_t b200_mla_peer_merge(const b200_mla_peer_merge_args* a, void* stream) {
+    if (!a) return fail(B200_MLA_ERR_INVALID_ARG, "args is NULL");
+    if (a->world != 1 && a->world != 2 && a->world != 4 && a->world != 8)
+        return fail(B200_MLA_ERR_UNSUPPORTED, "world must be 1, 2, 4 or 8 (got %d)", a->world);
+    if (a->rank < 0 || a->rank >= a->world) return fail(B200_MLA_ERR_INVALID_ARG, "rank %d outside [0, %d)", a->rank, a->world);
+    if (a->epoch == 0) return fail(B200_MLA_ERR_INVALID_ARG, "epoch starts at 1");
+    if (a->rows <= 0 || a->rows > 0x7fffffffLL) return fail(B200_MLA_ERR_INVALID_ARG, "rows must be in [1, 2^31)");
+    if (!a->bases || !a->out || ((uintptr_t)a->out & 7)) return fail(B200_MLA_ERR_INVALID_ARG, "bases and out (8-byte aligned) are required");
+    for (int i = 0; i < a->world; ++i)
+        if (!a->bases[i] || ((uintptr_t)a->bases[i] & 255)) return fail(B200_MLA_ERR_INVALID_ARG, "bases[%d] must be a 256-byte aligned device pointer", i);
+    void* ws = a->workspace;
+    if (!ws) {
+        const int rc = static_workspace_ptr(&ws);
+        if (rc != B200_MLA_OK) return rc;
+    }
+    const unsigned long long limit_ns = a->wait_limit_ms > 0 ? (unsigned long long)a->wait_limit_ms * 1000000ULL : 2000000000ULL;
+    cudaError_t e = launch_peer_merge(a->bases, a->world, a->rank, a->epoch, limit_ns, a->rows, a->out, (int*)ws, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(B200_MLA_ERR_CUDA, "peer merge launch failed: %s", cudaGetErrorString(e));
     return B200_MLA_OK;
 }
 

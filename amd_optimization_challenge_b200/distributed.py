@@ -177,3 +177,160 @@ def cuda_partial_fn(q, q_scale, kv_format: str, kv_local, kv_indptr_local, *, sm
                    kv_indices=kv_indices, kv_pos_offset=kv_pos_offset, kv_total_len=kv_total_len,
                    total_kv_hint=total_kv_hint, return_partial=True, partial_out=(out_o, out_lse), impl=impl)
     return fn
+
+
+# --------------------------------------------------------------------------------------------
+# split-KV across GPUs over peer memory: local partial -> fused signal + wait + merge kernel
+# --------------------------------------------------------------------------------------------
+
+class _DeviceSpan:
+    """A raw device range as something torch.as_tensor can wrap without a copy."""
+
+    def __init__(self, ptr: int, n_floats: int):
+        self.__cuda_array_interface__ = {"shape": (n_floats,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+class CudaPeerBackend:
+    """The exchange allocation and the merge kernel behind the C-ABI (b200_mla_peer_*)."""
+
+    def __init__(self, device):
+        from . import _cabi
+        self._c = _cabi
+        self.device = torch.device(device)
+
+    def exchange_bytes(self, rows: int) -> int:
+        return int(self._c.lib.b200_mla_peer_exchange_bytes(rows))
+
+    def partial_offset(self, rows: int, epoch: int) -> int:
+        return int(self._c.lib.b200_mla_peer_partial_offset(rows, epoch))
+
+    def alloc(self, rows: int):
+        import ctypes
+        base = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(self._c.PEER_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            self._c.check(self._c.lib.b200_mla_peer_alloc(rows, ctypes.byref(base), handle), "b200_mla_peer_alloc")
+        return int(base.value), bytes(handle.raw)
+
+    def open(self, handle: bytes) -> int:
+        import ctypes
+        base = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            self._c.check(self._c.lib.b200_mla_peer_open(handle, ctypes.byref(base)), "b200_mla_peer_open")
+        return int(base.value)
+
+    def close(self, base: int) -> None:
+        self._c.check(self._c.lib.b200_mla_peer_close(base), "b200_mla_peer_close")
+
+    def free(self, base: int) -> None:
+        self._c.check(self._c.lib.b200_mla_peer_free(base), "b200_mla_peer_free")
+
+    def floats(self, ptr: int, n: int) -> torch.Tensor:
+        return torch.as_tensor(_DeviceSpan(ptr, n), device=self.device)
+
+    def merge(self, bases, rank: int, epoch: int, rows: int, wait_limit_ms: int, workspace=None) -> torch.Tensor:
+        import ctypes
+        out = torch.empty(rows, V_DIM, dtype=torch.bfloat16, device=self.device)
+        arr = (ctypes.c_void_p * len(bases))(*bases)
+        a = self._c.PeerMergeArgs(world=len(bases), rank=rank, epoch=epoch, wait_limit_ms=wait_limit_ms, bases=arr, rows=rows,
+                                  out=out.data_ptr(), workspace=workspace.data_ptr() if workspace is not None else None)
+        with torch.cuda.device(self.device):
+            self._c.check(self._c.lib.b200_mla_peer_merge(ctypes.byref(a), torch.cuda.current_stream(self.device).cuda_stream),
+                          "b200_mla_peer_merge")
+        return out
+
+
+class PeerSplitKVDecoder:
+    """Cross-GPU split-KV without a collective call: every rank's partial (O || LSE) lives in an
+    exchange allocation the other ranks have mapped, and one kernel per rank signals, waits and
+    merges by reading the peers' memory (csrc/peer_merge.cu).  Same call shape as SplitKVDecoder.
+
+    The handles travel once, at construction, through `dist.all_gather_object`.  All ranks must
+    call `step` the same number of times (the step number is the kernels' rendezvous epoch).
+    `backend` is injectable so that the protocol (handle exchange, epochs, buffer parity) runs
+    under `gloo` on CPU with a shared-memory stand-in."""
+
+    def __init__(self, rows: int, heads: int, device, group=None, backend=None, wait_limit_ms: int = 0):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.rows, self.heads = rows, heads
+        self.n_rows = rows * heads
+        self.n_o = self.n_rows * V_DIM
+        self.backend = backend if backend is not None else CudaPeerBackend(device)
+        self.wait_limit_ms = wait_limit_ms
+        self.epoch = 0
+        # every rank learns whether every other rank got its allocation and its mappings: either all ranks
+        # hold a working decoder afterwards or all of them raise (nobody is left waiting for a peer that gave up)
+        self.bases = None
+        own, handle, err = None, None, None
+        try:
+            own, handle = self.backend.alloc(self.n_rows)
+        except Exception as e:                                   # noqa: BLE001 - reported to every rank below
+            err = f"rank {self.rank}: {e}"
+        opened = []
+        try:
+            handles = self._agree(handle, err)
+            err = None
+            try:
+                for r in range(self.world):
+                    opened.append(own if r == self.rank else self.backend.open(handles[r]))
+            except Exception as e:                               # noqa: BLE001
+                err = f"rank {self.rank}: {e}"
+            self._agree(True, err)                               # also: every mapping exists before the first signal
+        except Exception:
+            for r, b in enumerate(opened):
+                if r != self.rank:
+                    self.backend.close(b)
+            if own is not None:
+                self.backend.free(own)
+            raise
+        self.bases = opened
+
+    def _agree(self, payload, err):
+        """All-gather (payload, error string); raises on every rank if any rank reported an error, else returns
+        the list of all ranks' payloads."""
+        everyone = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(everyone, (payload, err), group=self.group)
+        else:
+            everyone[0] = (payload, err)
+        errors = [e for _, e in everyone if e]
+        if errors:
+            raise RuntimeError("peer-memory exchange is not available: " + "; ".join(errors))
+        return [p for p, _ in everyone]
+
+    def _views(self, epoch: int):
+        ptr = self.bases[self.rank] + self.backend.partial_offset(self.n_rows, epoch)
+        buf = self.backend.floats(ptr, self.n_o + self.n_rows)
+        return buf[: self.n_o].view(self.rows, self.heads, V_DIM), buf[self.n_o:].view(self.rows, self.heads)
+
+    def step(self, partial_fn: Callable, events=None, workspace=None):
+        """partial_fn(out_o, out_lse) fills this rank's normalised partial of this step; returns
+        the merged bf16 O [rows, heads, 512] on every rank.  `events`: two CUDA events recorded
+        before and after the merge kernel."""
+        self.epoch += 1
+        o, lse = self._views(self.epoch)
+        partial_fn(o, lse)
+        if events is not None:
+            events[0].record()
+        out = self.backend.merge(self.bases, self.rank, self.epoch, self.n_rows, self.wait_limit_ms, workspace)
+        if events is not None:
+            events[1].record()
+        return out.view(self.rows, self.heads, V_DIM)
+
+    def close(self):
+        """Unmap the peers and free the own allocation; collective (nobody may still be reading)."""
+        if self.bases is None:
+            return
+        if torch.cuda.is_available() and isinstance(self.backend, CudaPeerBackend):
+            torch.cuda.synchronize(self.backend.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for r, b in enumerate(self.bases):
+            if r != self.rank:
+                self.backend.close(b)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.backend.free(self.bases[self.rank])
+        self.bases = None

@@ -215,8 +215,8 @@ def sharded_modes(pkg, dist, rank, world, dev, kernel="auto", steps=30):
     with no collective; max over ranks).  Inputs are drawn on the GPU from one seed, so every rank holds the
     identical global problem and takes its shard of it."""
     import amd_optimization_challenge_b200.inputs as gen
-    from amd_optimization_challenge_b200.distributed import (SplitKVDecoder, cuda_partial_fn, shard_batch,
-                                                             split_kv_shard, token_balanced_partition)
+    from amd_optimization_challenge_b200.distributed import (PeerSplitKVDecoder, SplitKVDecoder, cuda_partial_fn,
+                                                             shard_batch, split_kv_shard, token_balanced_partition)
     out = {}
 
     # ---- config 3: token-balanced batch sharding, no data-path collective
@@ -274,6 +274,40 @@ def sharded_modes(pkg, dist, rank, world, dev, kernel="auto", steps=30):
                  "speedup_vs_n1": t1 / tn, "efficiency_vs_n1": t1 / tn / world,
                  "limiter": "stage-1 kernel" if s1 > 2 * (ag_us + merge_us) else "all-gather + merge",
                  "launch": "eager, queued behind a GPU spin; the all-gather is NCCL on the decode stream's order"}
+
+    # ---- config 4 again, the exchange and the merge fused into one kernel over peer memory (no collective call)
+    try:
+        pdec = PeerSplitKVDecoder(B * QL, w["heads"], dev)
+    except RuntimeError as e:                         # raised on every rank or on none
+        out["c4"]["peer_memory"] = {"unavailable": str(e)[:300]}
+        return out
+    ref_out = dec.step(part)
+    got = pdec.step(part)
+    diff = (got.float() - ref_out.float()).abs().max().reshape(1)
+    dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+    tp = _gpu_time_us(lambda: pdec.step(part), steps, dev, dist, world)
+    pair = [tuple(torch.cuda.Event(enable_timing=True) for _ in range(2)) for _ in range(10)]
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda._sleep(int(2e7))
+    for ev in pair:
+        pdec.step(part, events=ev)
+    torch.cuda.synchronize()
+    pm = torch.tensor([statistics.mean(e[0].elapsed_time(e[1]) for e in pair) * 1e3], device=dev)
+    dist.all_reduce(pm, op=dist.ReduceOp.MAX)
+    word = torch.zeros(1, dtype=torch.int32).pin_memory()
+    from amd_optimization_challenge_b200 import _cabi
+    _cabi.check(_cabi.lib.b200_mla_read_status(None, word.data_ptr(), torch.cuda.current_stream().cuda_stream), "status")
+    torch.cuda.synchronize()
+    st = torch.tensor([int(word[0])], device=dev)
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    out["c4"]["peer_memory"] = {
+        "mode": "cross-GPU split-KV, one fused signal + wait + merge kernel reading the peers' (O || LSE) over NVLink",
+        "us_per_step": tp, "tokens_per_s": tokens / (tp * 1e-6), "exchange_and_merge_us": float(pm[0]),
+        "nvlink_bytes_read_per_gpu": (world - 1) * dec.n * 4, "speedup_vs_n1": t1 / tp, "efficiency_vs_n1": t1 / tp / world,
+        "speedup_vs_all_gather_mode": tn / tp, "max_abs_diff_vs_all_gather_mode": float(diff[0]),
+        "status_bits_max_rank": int(st[0])}
+    pdec.close()
     return out
 
 

@@ -252,6 +252,49 @@ int32_t b200_mla_reset_status(void *workspace, void *stream);
  */
 int32_t b200_mla_set_stage1_events(void *start_event, void *stop_event);
 
+/*
+ * Cross-GPU split-KV over peer memory (one process per GPU on one NVLink / NVSwitch node).  The reference is
+ * single-GPU; what is exchanged and merged here is the split-KV reduce of mixed-mla/submission.py:257-294 with the
+ * splits living on different GPUs.  Rank r decodes its key range of every sequence with b200_mla_decode
+ * (kv_pos_offset / kv_total_len, out_o_f32 / out_lse) straight into its exchange allocation; b200_mla_peer_merge then
+ * signals the peers, waits for them with a time limit, reads their partials out of their memory with plain peer
+ * loads and writes the merged bf16 rows - no collective call, no staging copy.
+ *
+ *   b200_mla_peer_exchange_bytes(rows)   size of one rank's exchange allocation; rows = batch * q_len * heads
+ *   b200_mla_peer_alloc(rows, &base, handle)   cudaMalloc + zero + export: `handle` (B200_MLA_PEER_HANDLE_BYTES
+ *                                        bytes) goes to the other ranks by any host channel
+ *   b200_mla_peer_open(handle, &base)    map another rank's allocation into this process (CUDA IPC, peer access
+ *                                        enabled on first use); b200_mla_peer_close unmaps it
+ *   b200_mla_peer_partial_offset(rows, epoch)   byte offset, inside the allocation, of the (O [rows,512] fp32 ||
+ *                                        LSE [rows] fp32) partial of step `epoch` (two buffers, chosen by epoch & 1)
+ *   b200_mla_peer_merge(args, stream)    the fused signal + wait + merge kernel
+ *
+ * Protocol: all ranks call b200_mla_peer_merge once per decode step with the same `epoch`, which starts at 1 and
+ * grows by 1 per step, after the kernels that wrote this step's partial on the same stream.  bases[i] is rank i's
+ * allocation as mapped in the calling process (bases[rank] is its own).  A peer whose signal does not arrive
+ * within wait_limit_ms (0 = 2000) is merged with weight 0 and B200_MLA_STATUS_TIMEOUT is set in the status word of
+ * `workspace` (NULL = the built-in scratch); the kernel always returns.  world is 1, 2, 4 or 8.
+ * Each rank runs on its own GPU: two ranks must never share one GPU (their kernels wait on one another).
+ */
+#define B200_MLA_PEER_HANDLE_BYTES 64
+typedef struct {
+    int32_t world;
+    int32_t rank;
+    uint32_t epoch;
+    uint32_t wait_limit_ms;
+    const void *const *bases; /* host array [world] of device pointers */
+    int64_t rows;
+    void *out;                /* device bf16 [rows, 512] */
+    void *workspace;          /* holds the status word; NULL = built-in scratch */
+} b200_mla_peer_merge_args;
+int64_t b200_mla_peer_exchange_bytes(int64_t rows);
+int64_t b200_mla_peer_partial_offset(int64_t rows, uint32_t epoch);
+int32_t b200_mla_peer_alloc(int64_t rows, void **base, unsigned char *handle);
+int32_t b200_mla_peer_open(const unsigned char *handle, void **base);
+int32_t b200_mla_peer_close(void *base);
+int32_t b200_mla_peer_free(void *base);
+int32_t b200_mla_peer_merge(const b200_mla_peer_merge_args *args, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

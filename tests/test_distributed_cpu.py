@@ -137,7 +137,103 @@ def _batch_shard_worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("worker", [_split_kv_worker, _batch_shard_worker])
+class ShmPeerBackend:
+    """Host stand-in for the exchange allocations of the peer-memory mode: POSIX shared memory with the layout of
+    csrc/peer_merge.cu (64 flag words, then the partial of even steps, then the partial of odd steps), a "pointer"
+    being (mapping index << 40) + byte offset.  merge() follows the kernel's three steps: signal, bounded wait,
+    read the peers' partials and merge."""
+    FLAGS = 256
+
+    def __init__(self):
+        from multiprocessing import shared_memory
+        self._sm = shared_memory
+        self.maps = []
+
+    @staticmethod
+    def _part_bytes(rows):
+        return (rows * 513 * 4 + 255) // 256 * 256
+
+    def exchange_bytes(self, rows):
+        return self.FLAGS + 2 * self._part_bytes(rows)
+
+    def partial_offset(self, rows, epoch):
+        return self.FLAGS + (epoch & 1) * self._part_bytes(rows)
+
+    def _add(self, shm):
+        self.maps.append(shm)
+        return len(self.maps) << 40
+
+    def alloc(self, rows):
+        shm = self._sm.SharedMemory(create=True, size=self.exchange_bytes(rows))
+        shm.buf[:] = bytes(len(shm.buf))
+        return self._add(shm), shm.name.encode()
+
+    def open(self, handle):
+        return self._add(self._sm.SharedMemory(name=handle.decode()))
+
+    def _array(self, ptr, dtype, n):
+        return np.frombuffer(self.maps[(ptr >> 40) - 1].buf, dtype=dtype, count=n, offset=ptr & ((1 << 40) - 1))
+
+    def floats(self, ptr, n):
+        return torch.from_numpy(self._array(ptr, np.float32, n))
+
+    def close(self, base):
+        self.maps[(base >> 40) - 1].close()
+
+    def free(self, base):
+        shm = self.maps[(base >> 40) - 1]
+        shm.close(); shm.unlink()
+
+    def merge(self, bases, rank, epoch, rows, wait_limit_ms, workspace=None):
+        import time
+        for b in bases:
+            self._array(b, np.uint32, 64)[rank] = epoch
+        mine = self._array(bases[rank], np.uint32, 64)
+        t0 = time.time()
+        while any(int(mine[i]) < epoch for i in range(len(bases))):
+            if time.time() - t0 > (wait_limit_ms or 20000) / 1000:
+                raise TimeoutError("peer signal missing")
+            time.sleep(0.001)
+        off = self.partial_offset(rows, epoch)
+        o = torch.stack([self.floats(b + off, rows * 512).view(rows, 512) for b in bases])
+        l = torch.stack([self.floats(b + off + rows * 2048, rows) for b in bases])
+        return mo.merge_partials(o, l)[0].clone()
+
+
+def _peer_split_kv_worker(rank, world, port, ret):
+    """PeerSplitKVDecoder's protocol (handle exchange, epochs, the two partial buffers) with shared memory
+    standing in for mapped device memory; three steps with different queries, so both buffers are reused."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, QL, H, S = 2, 1, 16, 300
+        a, b = D.kv_range_partition(S, world)[rank]
+        n = b - a
+        idx = np.concatenate([np.arange(s * S + a, s * S + b) for s in range(B)]).astype(np.int32)
+        ip = np.arange(B + 1) * n
+        dec = D.PeerSplitKVDecoder(B * QL, H, "cpu", backend=ShmPeerBackend())
+        ok = len(dec.bases) == world and len(set(dec.bases)) == world
+        for step in range(3):
+            data = inputs.generate_input(B, QL, S, seed=20 + step, device="cpu", formats=("fp8",))
+            q, kvd, _, kvp, cfg = data
+            kf = mo.dequant_kv("fp8", kvd["fp8"])
+
+            def partial_fn(out_o, out_lse):
+                o, l = mo.mla_decode(q.float(), kf, ip, idx, cfg["sm_scale"], q_len=QL, kv_pos_offset=[a] * B,
+                                     kv_total_len=[S] * B)
+                out_o.copy_(o); out_lse.copy_(l)
+
+            merged = dec.step(partial_fn)
+            whole, _ = mo.mla_decode(q.float(), kf, kvp.numpy(), None, cfg["sm_scale"], q_len=QL)
+            ok = ok and merged.shape == (B * QL, H, 512) and torch.allclose(merged, whole, atol=1e-5)
+            ok = ok and dec.epoch == step + 1
+        dec.close()
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_split_kv_worker, _batch_shard_worker, _peer_split_kv_worker])
 def test_two_ranks_gloo(worker):
     world = 2
     with mp.Manager() as m:
