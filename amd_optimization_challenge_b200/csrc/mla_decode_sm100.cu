@@ -35,6 +35,7 @@
 // Role in the reference: the split-KV stage-1 kernels (mixed-mla/submission.py:122-250,
 // mixed-mla/versions/hip_mxfp4_v5/submission.py:214-656).
 #include <cuda.h>
+#include <cstdlib>
 #include <cstring>
 
 #include "sm100_ptx.cuh"
@@ -265,7 +266,37 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 // other gather threads only arrive.  A tile that reaches past the end of its sequence takes the copy loop
                 // below, which zero-fills the missing rows (TMA would bring whatever follows in memory, and zero
                 // probabilities do not neutralise non-finite bytes).
-                if (use_tma && pos0 + TILE <= wk.seq_len) {
+                if (use_tma == 2) {
+                    // Paged cache: the tile is TILE / 4 groups of four rows; one thread per group hands the four page
+                    // ids to the TMA unit, which fetches the rows' five panels (four 128-byte-wide, one 64-byte) with the
+                    // swizzle of the operand layout - 5 instructions per 4 rows instead of 144 16-byte copies.  A row past
+                    // the end of the sequence names the tile's first row instead (real cache bytes, finite; its
+                    // probabilities are zero).  Completion: bytes on the stage's mbarrier, announced per group.
+                    constexpr int G4 = TILE / 4;
+                    constexpr int G4S = PRODUCERS / G4 >= 8 ? 8 : (PRODUCERS / G4 >= 4 ? 4 : (PRODUCERS / G4 >= 2 ? 2 : 1));
+                    static_assert(G4 * 4 == TILE && G4 * G4S <= PRODUCERS, "one thread per group of four rows");
+                    const int gi = pt / G4S;
+                    if (pt % G4S == 0 && gi < G4) {
+                        const int s0 = slot_at(g, pos0, 0);
+                        int r[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int s = slot_at(g, pos0, 4 * gi + k);
+                            r[k] = (int)clamp_slot(p, s < 0 ? s0 : s);
+                        }
+                        mbar_arrive_expect_tx(&ms.kv_full[st], 4u * QK_DIM);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            tma_gather4_2d(stage_addr + j * PANEL_BYTES + gi * 512, &tmap_lat, 128 * j, r[0], r[1], r[2], r[3], &ms.kv_full[st]);
+                        tma_gather4_2d(stage_addr + 4 * PANEL_BYTES + gi * 256, &tmap_rope, 512, r[0], r[1], r[2], r[3], &ms.kv_full[st]);
+                    } else {
+                        mbar_arrive(&ms.kv_full[st]);
+                    }
+                    prefetch_ids(g + NS);
+                    if (q_due >= 0 && (g >= q_due || g == n_total - 1)) flush_q();
+                    continue;
+                }
+                if (use_tma == 1 && pos0 + TILE <= wk.seq_len) {
                     if (pt == 0) {
                         mbar_arrive_expect_tx(&ms.kv_full[st], (uint32_t)STAGE_BYTES);
                         const int row = wk.seq_base + pos0;
@@ -645,19 +676,22 @@ static cudaError_t launch_n(const MlaParams& p, int* status, cudaStream_t stream
     memset(&lat, 0, sizeof(lat));
     memset(&rope, 0, sizeof(rope));
     int use_tma = 0;
-    if (p.kv_indices == nullptr && p.kv_codes_stride % 16 == 0 && p.kv_codes_stride >= QK_DIM && p.num_slots > 0 &&
-        p.num_slots < (1LL << 31)) {
+    const char* off = getenv("B200_MLA_DISABLE_TMA");                 // testing aid: "1" keeps every tile on the copy loop
+    if (!(off && off[0] == '1') && ((uintptr_t)p.kv_codes & 15) == 0 && p.kv_codes_stride % 16 == 0 &&
+        p.kv_codes_stride >= QK_DIM && p.num_slots > 0 && p.num_slots < (1LL << 31)) {
+        // contiguous cache: boxes of a whole tile; page table: boxes of one row, fetched four at a time by row index
+        const int box_rows = p.kv_indices == nullptr ? L::TILE : 1;
         MapEntry* hit = nullptr;
         for (MapEntry& m : cache)
-            if (m.base == p.kv_codes && m.slots == p.num_slots && m.stride == p.kv_codes_stride && m.tile == L::TILE) hit = &m;
+            if (m.base == p.kv_codes && m.slots == p.num_slots && m.stride == p.kv_codes_stride && m.tile == box_rows) hit = &m;
         if (!hit) {
             hit = &cache[next];
             next = (next + 1) % 4;
-            hit->base = p.kv_codes; hit->slots = p.num_slots; hit->stride = p.kv_codes_stride; hit->tile = L::TILE;
-            hit->ok = make_cache_map(&hit->lat, p, 128, L::TILE, CU_TENSOR_MAP_SWIZZLE_128B) &&
-                      make_cache_map(&hit->rope, p, 64, L::TILE, CU_TENSOR_MAP_SWIZZLE_64B);
+            hit->base = p.kv_codes; hit->slots = p.num_slots; hit->stride = p.kv_codes_stride; hit->tile = box_rows;
+            hit->ok = make_cache_map(&hit->lat, p, 128, box_rows, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                      make_cache_map(&hit->rope, p, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_64B);
         }
-        use_tma = hit->ok;
+        use_tma = hit->ok ? (p.kv_indices == nullptr ? 1 : 2) : 0;
         if (use_tma) { lat = hit->lat; rope = hit->rope; }
     }
     dim3 grid(p.num_ctas, p.rows / N);

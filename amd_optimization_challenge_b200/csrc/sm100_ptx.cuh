@@ -69,6 +69,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap,
                  ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
+// Tiled 2-D TMA gather of FOUR rows (y0..y3, any order, any distance) of the map's tensor, `box width` bytes each starting
+// at byte x (a multiple of 16), into four consecutive rows at dst_smem; the map's box is {width, 1}.  The swizzle of the
+// map is applied as for an ordinary tile.  Completion is counted in bytes (4 x width) on `bar`.  This GPU's memory only.
+__device__ __forceinline__ void tma_gather4_2d(uint32_t dst_smem, const void* tmap, int x, int y0, int y1, int y2, int y3, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                 ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

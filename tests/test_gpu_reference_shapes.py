@@ -175,3 +175,22 @@ def test_status_entry_points_through_the_c_abi(pkg):
     assert lib.b200_mla_read_status(None, word.data_ptr(), stream) == 0
     torch.cuda.synchronize()
     assert int(word[0]) in (0, 1, 2, 3)
+
+
+@pytest.mark.parametrize("shuffle", [False, True])
+@pytest.mark.parametrize("heads,lens", [(16, [300, 77, 112, 5, 1000, 113]), (32, [224, 7, 450])])
+def test_tma_tiles_equal_copy_loop_tiles(pkg, monkeypatch, shuffle, heads, lens):
+    """The FP8 kernel fills its operand stages in three ways - tiled TMA boxes (contiguous cache), TMA row gathers by
+    page id (page table) and 16-byte copies (fallback; B200_MLA_DISABLE_TMA=1 forces it).  The stages must hold the
+    same bytes, so the outputs are identical bit for bit; ragged lengths put rows past the end into the last tiles."""
+    data = pkg.generate_input(len(lens), 1, max(lens), seed=91, kv_lens=lens, shuffle_pages=shuffle, num_heads=heads,
+                              formats=("fp8",))
+    monkeypatch.delenv("B200_MLA_DISABLE_TMA", raising=False)
+    a = _run(pkg, data, "fp8", "fp8", "tcgen05")
+    torch.cuda.synchronize()
+    monkeypatch.setenv("B200_MLA_DISABLE_TMA", "1")
+    b = _run(pkg, data, "fp8", "fp8", "tcgen05")
+    torch.cuda.synchronize()
+    monkeypatch.delenv("B200_MLA_DISABLE_TMA")
+    assert torch.equal(a, b)
+    assert_close(a, oracle_for_data(data, "fp8", "fp8"), tight=1.5e-2)
