@@ -76,6 +76,19 @@ __device__ __forceinline__ void tma_gather4_2d(uint32_t dst_smem, const void* tm
     asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
                  ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(smem_u32(bar)) : "memory");
 }
+// The same with an L2 eviction policy for the fetched lines (see l2_evict_first_policy).
+__device__ __forceinline__ void tma_gather4_2d_hint(uint32_t dst_smem, const void* tmap, int x, int y0, int y1, int y2, int y3, uint64_t* bar,
+                                                    uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;"
+                 ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(smem_u32(bar)), "l"(policy) : "memory");
+}
+// Policy word for data that is read once (the cache rows): its lines are the first to leave L2, so the streaming
+// megabytes do not push out what every launch needs again - the kernels' code, Q, the page table.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -206,6 +219,45 @@ __device__ __forceinline__ void reduce_cols_128(float (&v)[NC], float (*red)[32]
         v[c] = IS_MAX ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : (a0 + a1) + (a2 + a3);
     }
     named_bar_sync(bar_id, 128);
+}
+
+// The same reduction in a tenth of the instructions, for code that runs once per sequence, where what counts is how many
+// instruction lines the first pass has to fetch: the values go through a scratch area of NC/2 x 128 floats (column-major:
+// thread t of the group = row t), NC/2 columns per round; 128 / (NC/2) threads share a column, each folds a contiguous
+// run of NC/2 rows read as 16-byte vectors, a few shuffles finish the column, one lane per column publishes it in `red`
+// (>= NC floats).  Four named barriers; the caller owns `scratch` for the duration.  t = thread index inside the group.
+template <int NC, bool IS_MAX>
+__device__ __forceinline__ void reduce_cols_128_scratch(float (&v)[NC], float* scratch, float* red, int t, int bar_id) {
+    constexpr int H = NC / 2, TPC = 128 / H;          // columns per round, threads per column (= rows per thread: H)
+    static_assert(NC % 8 == 0 && H * TPC == 128, "column split");
+    const int col = t / TPC, seg = t % TPC;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+#pragma unroll
+        for (int c = 0; c < H; ++c) scratch[c * 128 + t] = v[r * H + c];
+        named_bar_sync(bar_id, 128);
+        const float4* src = reinterpret_cast<const float4*>(scratch + col * 128 + seg * H);
+        float4 a = src[0];
+#pragma unroll
+        for (int i = 1; i < H / 4; ++i) {
+            const float4 b = src[i];
+            a.x = IS_MAX ? fmaxf(a.x, b.x) : a.x + b.x; a.y = IS_MAX ? fmaxf(a.y, b.y) : a.y + b.y;
+            a.z = IS_MAX ? fmaxf(a.z, b.z) : a.z + b.z; a.w = IS_MAX ? fmaxf(a.w, b.w) : a.w + b.w;
+        }
+        float x = IS_MAX ? fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)) : (a.x + a.y) + (a.z + a.w);
+#pragma unroll
+        for (int o = TPC / 2; o >= 1; o >>= 1) {
+            const float y = __shfl_xor_sync(0xffffffffu, x, o);
+            x = IS_MAX ? fmaxf(x, y) : x + y;
+        }
+        if (seg == 0) red[r * H + col] = x;
+        named_bar_sync(bar_id, 128);
+    }
+#pragma unroll
+    for (int c = 0; c < NC; c += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(red + c);
+        v[c] = q.x; v[c + 1] = q.y; v[c + 2] = q.z; v[c + 3] = q.w;
+    }
 }
 
 __device__ __forceinline__ float ex2(float x) {
