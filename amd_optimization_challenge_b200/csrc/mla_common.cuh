@@ -89,6 +89,18 @@ __device__ __forceinline__ int span_begin(const int* prefix, int batch, int w, i
     const int b = seq_of_unit(prefix, batch, u);
     return max(prefix[b], u - SEQ_UNITS * (b + 1));
 }
+// The same, also returning a sequence b_out <= the sequence of the returned tile (Walker::init_at starts from it,
+// which saves the roles a binary search of their own at their start).
+__device__ __forceinline__ int span_begin_seq(const int* prefix, int batch, int w, int G, int& b_out) {
+    b_out = 0;
+    if (w >= G) return prefix[batch];
+    const int tu = total_units(prefix[batch], batch);
+    const int u = ((unsigned long long)(unsigned)w * (unsigned)tu >> 32) == 0 ? (int)(((unsigned)w * (unsigned)tu) / (unsigned)G)
+                                                                            : (int)(((long long)w * tu) / G);
+    const int b = seq_of_unit(prefix, batch, u);
+    b_out = b;
+    return max(prefix[b], u - SEQ_UNITS * (b + 1));
+}
 // CTA whose span contains tile t of sequence b (unit t + K*(b+1)).
 __device__ __forceinline__ int cta_of_tile(int t, int b, int units, int G) {
     return (int)((((long long)(t + SEQ_UNITS * (b + 1) + 1) * G + units - 1) / units) - 1);
@@ -186,6 +198,13 @@ struct Walker {
     int pair;                               // (CTA, sequence) pairs started so far, minus one
     __device__ __forceinline__ void init(const int* prefix, int batch, int t_begin) {
         b = seq_of_tile(prefix, batch, t_begin) - 1;
+        seq_t0 = 0; seq_t1 = -1;
+        seq_base = seq_len = page_base = pos_off = tot_len = 0;
+        pair = -1;
+    }
+    // Start from a known sequence b0 <= the sequence of the first tile that will be sought.
+    __device__ __forceinline__ void init_at(int b0) {
+        b = b0 - 1;
         seq_t0 = 0; seq_t1 = -1;
         seq_base = seq_len = page_base = pos_off = tot_len = 0;
         pair = -1;

@@ -125,6 +125,10 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
         for (unsigned int i = lo + tid * 32; i < hi; i += 64 * 32)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kv_indices + i));
     }
+    if (tid == L::FIRST_PRODUCER && use_tma) {                 // the copy engine's descriptors: fetched while the schedule is computed
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_lat) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_rope) : "memory");
+    }
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) { mbar_init(&ms.kv_full[i], PRODUCERS); mbar_init(&ms.kv_empty[i], 1); }
         for (int i = 0; i < 2; ++i) {
@@ -145,7 +149,8 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
     if (w == 0 && blockIdx.y == 0)
         for (int i = tid; i <= p.batch; i += THREADS) p.tile_prefix[i] = prefix[i];
 
-    const int t_begin = TT > 0 ? span_begin(prefix, p.batch, w, G) : 0, t_end = TT > 0 ? span_begin(prefix, p.batch, w + 1, G) : 0;
+    int b_begin = 0;
+    const int t_begin = TT > 0 ? span_begin_seq(prefix, p.batch, w, G, b_begin) : 0, t_end = TT > 0 ? span_begin(prefix, p.batch, w + 1, G) : 0;
     const int n_total = t_end - t_begin;                          // tiles of this CTA; tile index g = 0..n_total-1
 
     const float q_sc = block_q_scale(q_amax_local, p.q_scale, QCAST, &ms.q_amax);
@@ -157,7 +162,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             // One stage = TILE tokens x 36 sixteen-byte columns.  Consecutive threads take consecutive
             // columns, so a warp instruction reads 512 contiguous bytes of (at most two) rows.
             const int pt = tid - L::FIRST_PRODUCER;
-            Walker wk; wk.init(prefix, p.batch, t_begin);
+            Walker wk; wk.init_at(b_begin);
             Walker wn = wk;                                       // NS tiles ahead, for the page-table prefetch
             const bool paged = p.kv_indices != nullptr;
             // Page ids of tile g -> ring entry g % SLOT_RING by 4-byte cp.async, NS tiles before the tile's rows are
@@ -390,7 +395,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 const uint64_t d_pv_a = make_desc(smem_base, PANEL_BYTES, 1024, SWIZZLE_128B);         // + stage
                 const uint64_t d_pv_b = make_desc(smem_base + L::OFF_P, 128, MMA_M * 16, SWIZZLE_NONE); // + buffer
                 Walker wq, wv;                                    // the QK stream runs ahead of the PV stream
-                wq.init(prefix, p.batch, t_begin);
+                wq.init_at(b_begin);
                 wv = wq;
                 // S^T[128 tok x N] = K . Q^T for tile g
                 auto issue_qk = [&](int g, bool dry) {
@@ -486,7 +491,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             const float score_scale = p.sm_scale * LOG2E * q_sc * kv_sc;
             const float out_scale = kv_sc;
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-            Walker wk; wk.init(prefix, p.batch, t_begin);
+            Walker wk; wk.init_at(b_begin);
             // nm[c] = P_SCALE_LOG2 - (reference maximum of column c); +inf while the column has seen no key
             float nm[N], l_acc[N];
             // token position pos is visible to the rows of 16-column chunk q iff pos < lim[q]
@@ -543,7 +548,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     float mx[N];
 #pragma unroll
                     for (int c = 0; c < N; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : s[c] * score_scale;
-                    reduce_cols_128_scratch<N, true>(mx, reinterpret_cast<float*>(pbuf), &ms.red[0][0], tid, 1);
+                    reduce_cols_128_scratch<N, true, 2>(mx, reinterpret_cast<float*>(pbuf), &ms.red[0][0], tid, 1);
                     float f[N];
                     bool any = false;
 #pragma unroll
@@ -606,7 +611,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
                     mbar_wait(&ms.p_empty[sb], g / 2, abort_flag);
                     tc_fence_after();
-                    reduce_cols_128_scratch<N, false>(l_acc, reinterpret_cast<float*>(pbuf), &ms.red[0][0], tid, 1);   // PV(g) is done: P buffer free
+                    reduce_cols_128_scratch<N, false, 2>(l_acc, reinterpret_cast<float*>(pbuf), &ms.red[0][0], tid, 1);   // PV(g) is done: P buffer free
                     const bool whole = (t_begin <= wk.seq_t0) && (wk.seq_t1 <= t_end);
                     const int slot = w + wk.b;
                     float inv[N];

@@ -350,6 +350,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 // QK_PARTS > 1 would issue it in pieces with PVs in between; measured slower (alternating the two MMA
                 // shapes costs more than the PV gains), so it stays in one piece.
                 constexpr int QK_PARTS = 1;
+                static_assert(QK_PARTS == 1, "issue_qk issues the whole product");
                 auto issue_qk = [&](int g, int part) {
                     const int st = g % NS, sb = g & 1;
                     if (part == 0) {
@@ -357,17 +358,19 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                         tc_fence_after();
                     }
                     const uint32_t d_lat = tmem + sb * C::SC, d_rope = d_lat + (C::ROPE_SEP ? NQ : 0);
+                    // panel by panel, the panel loop not unrolled: the issue code stays a few hundred bytes, which is what
+                    // the first pass through it (instruction fetch, on every CTA's critical path) pays for
+#pragma unroll 1
+                    for (int j = 0; j < 4; ++j) {
 #pragma unroll
-                    for (int kk = 0; kk < 18 / QK_PARTS; ++kk) {
-                        const int k = part * (18 / QK_PARTS) + kk;
-                        if (k < 16) {
-                            umma_f8_elect(d_lat, desc_advance(d_qk_a, st * STAGE_BYTES + (k >> 2) * PANEL_BYTES + (k & 3) * 32),
-                                    desc_advance(d_qk_b, (k >> 2) * C::Q_PANEL_BYTES + (k & 3) * 32), IDESC_QK, k > 0 ? 1u : 0u);
-                        } else {
-                            umma_f8_elect(d_rope, desc_advance(d_qk_a_rope, st * STAGE_BYTES + (k - 16) * 32),
-                                    desc_advance(d_qk_b_rope, (k - 16) * 32), IDESC_QK, (!C::ROPE_SEP || k > 16) ? 1u : 0u);
-                        }
+                        for (int k = 0; k < 4; ++k)
+                            umma_f8_elect(d_lat, desc_advance(d_qk_a, st * STAGE_BYTES + j * PANEL_BYTES + k * 32),
+                                          desc_advance(d_qk_b, j * C::Q_PANEL_BYTES + k * 32), IDESC_QK, (j | k) ? 1u : 0u);
                     }
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)
+                        umma_f8_elect(d_rope, desc_advance(d_qk_a_rope, st * STAGE_BYTES + k * 32), desc_advance(d_qk_b_rope, k * 32),
+                                      IDESC_QK, (!C::ROPE_SEP || k > 0) ? 1u : 0u);
                     if (part == QK_PARTS - 1) {
                         umma_commit_elect(&ms.s_full[sb]);
                         // last tile of this (CTA, sequence) pair: the Q buffer is free once these MMAs have run
@@ -384,7 +387,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     // any more, and (ROWS_EARLY) the transform warps of those rows may write the tile after next.
                     // MERGED: the hi and the lo term of P are two k-steps into the same O columns (the lo chunks follow
                     // the hi chunks in the P buffer); otherwise they are the two halves of the MMA's 2N columns.
-#pragma unroll
+#pragma unroll 1
                     for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
                         for (int half = 0; half < (C::MERGED ? 2 : 1); ++half) {
@@ -679,11 +682,15 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
 #pragma unroll
                     for (int c = 0; c < NC; ++c) f[c] = 1.0f;
                     if (recenter) {
+                        // the warpgroup's hi chunks of this tile's P buffer (free once the PV that read it last has
+                        // completed) are the scratch area of the column reduction
+                        mbar_wait(&ms.p_empty[g % C::P_BUFS], g / C::P_BUFS - 1, abort_flag);
+                        float* scratch = reinterpret_cast<float*>(smem + C::OFF_P + (g % C::P_BUFS) * C::P_BUF_BYTES + (col0 / 16) * (TILE * 16));
                         float sv[NC], mx[NC];
                         load_scores(sv);
 #pragma unroll
                         for (int c = 0; c < NC; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : sv[c];
-                        reduce_cols_128<NC, true>(mx, ms.red[sg], warp & 3, lane, bar_id);
+                        reduce_cols_128_scratch<NC, true, 4>(mx, scratch, &ms.red[sg][0][0], tok, bar_id);
 #pragma unroll
                         for (int c = 0; c < NC; ++c) {
                             const float m_old = P_SCALE_LOG2 - nm(c);                 // -inf for a fresh column
@@ -705,8 +712,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                         // O holds the sequence's earlier tiles once PV(g-1) has completed; nothing else touches it until P(g) is published
                         mbar_wait(&ms.p_empty[(g - 1) % C::P_BUFS], (g - 1) / C::P_BUFS, abort_flag);
                         tc_fence_after();
-#pragma unroll
-                        for (int jb = 0; jb < 4; ++jb) {
+#pragma unroll 1
+                        for (int jb = 0; jb < 4; ++jb) {                         // rare path: kept small, not unrolled
 #pragma unroll
                             for (int h = 0; h < (C::MERGED ? 1 : 2); ++h) {      // side by side: the hi and the lo columns
 #pragma unroll
@@ -763,7 +770,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
                     mbar_wait(&ms.p_empty[pb], g / C::P_BUFS, abort_flag);
                     tc_fence_after();
-                    reduce_cols_128<NC, false>(l_acc, ms.red[sg], warp & 3, lane, bar_id);
+                    reduce_cols_128_scratch<NC, false, 4>(l_acc, reinterpret_cast<float*>(pbuf + (col0 / 16) * (TILE * 16)), &ms.red[sg][0][0], tok,
+                                                          bar_id);                   // PV(g) is done: the P buffer is free
                     const bool whole = (t_begin <= wk.seq_t0) && (wk.seq_t1 <= t_end);
                     const int slot = w + wk.b;
                     const float out_scale = C::XF ? pow2i(e_run - E_BIAS) : kv_tensor_scale;
@@ -776,8 +784,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     __nv_bfloat16* dst_bf16 = whole ? p.out : nullptr;
                     if (dst_f32) dst_f32 += orow0 * V_DIM + tok;
                     if (dst_bf16) dst_bf16 += orow0 * V_DIM + tok;
-#pragma unroll
-                    for (int jb = 0; jb < 4; ++jb) {
+#pragma unroll 1
+                    for (int jb = 0; jb < 4; ++jb) {                             // once per sequence: code size before speed
 #pragma unroll
                         for (int c0 = 0; c0 < NC; c0 += 16) {
                             float ohi[16], olo[16];

@@ -221,18 +221,19 @@ __device__ __forceinline__ void reduce_cols_128(float (&v)[NC], float (*red)[32]
     named_bar_sync(bar_id, 128);
 }
 
-// The same reduction in a tenth of the instructions, for code that runs once per sequence, where what counts is how many
-// instruction lines the first pass has to fetch: the values go through a scratch area of NC/2 x 128 floats (column-major:
-// thread t of the group = row t), NC/2 columns per round; 128 / (NC/2) threads share a column, each folds a contiguous
-// run of NC/2 rows read as 16-byte vectors, a few shuffles finish the column, one lane per column publishes it in `red`
-// (>= NC floats).  Four named barriers; the caller owns `scratch` for the duration.  t = thread index inside the group.
-template <int NC, bool IS_MAX>
+// The same reduction in a fraction of the instructions, for code that runs once per sequence, where what counts is how
+// many instruction lines the first pass has to fetch: the values go through a scratch area of NC/R x 128 floats
+// (column-major: thread t of the group = row t), NC/R columns per round, R rounds; 128 / (NC/R) threads share a column,
+// each folds a contiguous run of rows read as 16-byte vectors, a few shuffles finish the column, one lane per column
+// publishes it in `red` (>= NC floats).  2R named barriers; the caller owns `scratch` for the duration.
+// t = thread index inside the group.
+template <int NC, bool IS_MAX, int R>
 __device__ __forceinline__ void reduce_cols_128_scratch(float (&v)[NC], float* scratch, float* red, int t, int bar_id) {
-    constexpr int H = NC / 2, TPC = 128 / H;          // columns per round, threads per column (= rows per thread: H)
-    static_assert(NC % 8 == 0 && H * TPC == 128, "column split");
+    constexpr int H = NC / R, TPC = 128 / H;          // columns per round, threads per column (= rows per thread: H)
+    static_assert(NC % R == 0 && H % 4 == 0 && H * TPC == 128 && TPC <= 32, "column split");
     const int col = t / TPC, seg = t % TPC;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < R; ++r) {
 #pragma unroll
         for (int c = 0; c < H; ++c) scratch[c * 128 + t] = v[r * H + c];
         named_bar_sync(bar_id, 128);
