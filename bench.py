@@ -55,7 +55,7 @@ KV_ROW_BYTES = {"fp8": 576, "mxfp4": 306, "hybrid": 336}
 MODES = {"c1": "replica", "c2": "replica", "c3": "batch_shard", "c4": "split_kv"}
 # DRAM bytes read + written by one stage-1 launch, from one ncu capture of that workload's kernel on one GPU
 # (profiles/ holds each capture's summary and command; regenerate them together with the kernels).
-NCU_TRAFFIC_BYTES = {"c1": 83.3e6, "c2": 190.0e6, "c3": 770.0e6, "c4": 428.0e6}
+NCU_TRAFFIC_BYTES = {"c1": 79.4e6, "c2": 191.0e6, "c3": 571.7e6, "c4": 431.8e6}
 L2_BYTES = 126 << 20
 
 
