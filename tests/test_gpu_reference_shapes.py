@@ -194,3 +194,42 @@ def test_tma_tiles_equal_copy_loop_tiles(pkg, monkeypatch, shuffle, heads, lens)
     monkeypatch.delenv("B200_MLA_DISABLE_TMA")
     assert torch.equal(a, b)
     assert_close(a, oracle_for_data(data, "fp8", "fp8"), tight=1.5e-2)
+
+
+@pytest.mark.parametrize("impl", ["generic", "tcgen05"])
+@pytest.mark.parametrize("kv_format,q_format", [("fp8", "fp8"), ("mxfp4", "bf16")])
+@pytest.mark.parametrize("gap_log2", [12.0, 15.0])
+def test_one_dominant_key_and_a_long_coherent_tail(pkg, impl, kv_format, q_format, gap_log2):
+    """A sink-like distribution: one key whose probability dominates and 8192 keys `gap_log2` binades below it
+    whose values all point the same way, so that their total mass (8192 * 2^-gap) moves the output visibly
+    (by 0.25 / 1.25 of the value gap at 15 binades).  The tcgen05 kernels carry probabilities as two e4m3 terms; this
+    is the case that shows whether the small ones survive (they do down to about 17 binades)."""
+    import math
+    from amd_optimization_challenge_b200 import inputs
+    g = torch.Generator().manual_seed(5)
+    S, H = 8193, 16
+    u = torch.randn(576, generator=g)
+    u = u / u.norm()
+    sm_scale = 576 ** -0.5
+    a = 1.0 / sm_scale                                              # q = a u  ->  score = beta of the key
+    gap = gap_log2 * math.log(2.0)
+    kv = torch.empty(S, 576)
+    kv[0] = (gap / 2) * u
+    kv[1:] = (-gap / 2) * u + 0.002 * torch.randn(S - 1, 576, generator=g)
+    kv = kv.to(torch.bfloat16).view(S, 1, 576)
+    q = (a * u).to(torch.bfloat16).view(1, 1, 576).expand(1, H, 576).contiguous()
+    q = q + (0.05 * torch.randn(1, H, 576, generator=g)).to(torch.bfloat16)
+    planes = inputs.quantize_fp8(kv) if kv_format == "fp8" else inputs.quantize_mxfp4(kv)
+    kvd = {kv_format: tuple(t.cuda() for t in planes)}
+    ip = torch.tensor([0, S], dtype=torch.int32).cuda()
+    cfg = {"batch_size": 1, "num_heads": H, "q_seq_len": 1, "kv_seq_len": S, "sm_scale": sm_scale,
+           "kv_format": kv_format, "q_format": q_format, "impl": impl}
+    data = (q.cuda(), kvd, torch.tensor([0, 1], dtype=torch.int32).cuda(), ip, cfg)
+    out = pkg.custom_kernel(data)
+    torch.cuda.synchronize()
+    ref = oracle_for_data(data, kv_format, q_format)
+    assert_close(out, ref, tight=2e-2)
+    # the tail matters in this problem: without it the output would sit at the dominant key's value
+    if gap_log2 >= 15.0:
+        v0 = kv[0, 0, :512].float()
+        assert (ref[0, 0].float().cpu() - v0).abs().max() > 0.1 * v0.abs().max()
