@@ -40,14 +40,6 @@
 
 #include "sm100_ptx.cuh"
 
-// bit 0: warm-up issue of one QK and one PV block by the MMA warp; bit 1: warm-up pass of the softmax warps
-#ifndef B200MLA_WARM
-#define B200MLA_WARM 0
-#endif
-#ifndef B200MLA_EVICT_FIRST
-#define B200MLA_EVICT_FIRST 1
-#endif
-
 namespace b200mla {
 namespace sm100 {
 
@@ -307,18 +299,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     if (g4_issuer) {
                         const int (&r)[4] = r4;
                         mbar_arrive_expect_tx(&ms.kv_full[st], 4u * QK_DIM);
-#if B200MLA_EVICT_FIRST
                         const uint64_t pol = l2_evict_first_policy();
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             tma_gather4_2d_hint(stage_addr + j * PANEL_BYTES + gi * 512, &tmap_lat, 128 * j, r[0], r[1], r[2], r[3], &ms.kv_full[st], pol);
                         tma_gather4_2d_hint(stage_addr + 4 * PANEL_BYTES + gi * 256, &tmap_rope, 512, r[0], r[1], r[2], r[3], &ms.kv_full[st], pol);
-#else
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            tma_gather4_2d(stage_addr + j * PANEL_BYTES + gi * 512, &tmap_lat, 128 * j, r[0], r[1], r[2], r[3], &ms.kv_full[st]);
-                        tma_gather4_2d(stage_addr + 4 * PANEL_BYTES + gi * 256, &tmap_rope, 512, r[0], r[1], r[2], r[3], &ms.kv_full[st]);
-#endif
                     } else {
                         mbar_arrive(&ms.kv_full[st]);
                     }
@@ -398,7 +383,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 wq.init_at(b_begin);
                 wv = wq;
                 // S^T[128 tok x N] = K . Q^T for tile g
-                auto issue_qk = [&](int g, bool dry) {
+                auto issue_qk = [&](int g) {
                     const int st = g % NS, sb = g & 1;
                     fence_proxy_async();       // stage and Q were written by cp.async (generic proxy); the MMA reads through the async proxy
                     tc_fence_after();
@@ -417,13 +402,12 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     for (int k = 0; k < 2; ++k)
                         umma_f8_elect(tmem + L::TMEM_S + sb * N, desc_advance(d_qk_a_rope, st * STAGE_BYTES + k * 32),
                                       desc_advance(b0, 4 * L::Q_PANEL_BYTES + k * 32), IDESC_QK, 1u);
-                    if (dry) return;
                     umma_commit_elect(&ms.s_full[sb]);
                     // last tile of this (CTA, sequence) pair: its Q buffer is free once these MMAs have run
                     if (t_begin + g + 1 == min(t_end, wq.seq_t1)) umma_commit_elect(&ms.q_empty[wq.pair & 1]);
                 };
                 // O^T += V^T P^T over the 128 tokens of tile g, four blocks of 128 dims
-                auto issue_pv = [&](int g, bool first, bool dry) {
+                auto issue_pv = [&](int g, bool first) {
                     const int st = g % NS, pb = g & 1;
                     tc_fence_after();
                     const uint64_t a0 = desc_advance(d_pv_a, st * STAGE_BYTES);
@@ -436,7 +420,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                                     desc_advance(b0, kk * 32 * 16), IDESC_PV, (first && kk == 0) ? 0u : 1u);
                         }
                     }
-                    if (dry) return;
                     umma_commit_elect(&ms.kv_empty[st]);
                     umma_commit_elect(&ms.p_empty[pb]);
                 };
@@ -444,15 +427,6 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 // QK of the next tile as soon as it has landed, its S buffer is free and its Q is in place.
                 int nq = 0, nv = 0;
                 bool q_first = wq.seek(p, prefix, t_begin), v_first = wv.seek(p, prefix, t_begin);
-                // Warm-up while the first tile is on its way: one QK and one PV block are issued on whatever the buffers
-                // hold and never committed.  Their results land in S buffer 1 and in O, which the first real QK(1) / the
-                // first real PV overwrite (accumulate off); what they buy is that the instructions, descriptors and
-                // kernel parameters of both issue paths are cached when tile 0 arrives (the first pass through cold
-                // code measured 6000 + 3300 cycles against 900 + 800 afterwards, on the critical path of every CTA).
-                if (B200MLA_WARM & 1) {
-                    issue_qk(1, true);
-                    issue_pv(1, true, true);
-                }
                 long long t_idle = clock64();
                 uint32_t spins = 0;
                 while (nv < n_total) {
@@ -476,11 +450,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     }
                     __syncwarp();
                     if (pv_ready) {
-                        issue_pv(nv, v_first, false);
+                        issue_pv(nv, v_first);
                         ++nv; spins = 0;
                         if (nv < n_total) v_first = wv.seek(p, prefix, t_begin + nv);
                     } else if (qk_ready) {
-                        issue_qk(nq, false);
+                        issue_qk(nq);
                         ++nq; spins = 0;
                         if (nq < n_total) q_first = wq.seek(p, prefix, t_begin + nq);
                     }
@@ -497,15 +471,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
             // token position pos is visible to the rows of 16-column chunk q iff pos < lim[q]
             // (heads is a multiple of 16, so the query index j is constant inside a chunk)
             int lim[N / 16], lim_min = 0;
-            // g = -1 is a warm-up pass over the same instructions while the first tile is on its way: it reads whatever
-            // S buffer 1 holds, takes the re-centering path like every first tile, writes P buffer 1 (rewritten by
-            // tile 1) and touches no mbarrier; all its state is reset by the first real tile (first == true).
-            for (int g = (B200MLA_WARM & 2) ? -1 : 0; g < n_total; ++g) {
-                const bool dry = g < 0;
+            for (int g = 0; g < n_total; ++g) {
                 const int sb = g & 1;
-                const bool first = dry ? true : wk.seek(p, prefix, t_begin + g);
-                const bool last = !dry && t_begin + g + 1 == min(t_end, wk.seq_t1);
-                const int pos_first = dry ? 0 : (t_begin + g - wk.seq_t0) * TILE;
+                const bool first = wk.seek(p, prefix, t_begin + g);
+                const bool last = t_begin + g + 1 == min(t_end, wk.seq_t1);
+                const int pos_first = (t_begin + g - wk.seq_t0) * TILE;
                 if (first) {
 #pragma unroll
                     for (int c = 0; c < N; ++c) { nm[c] = INFINITY; l_acc[c] = 0.0f; }
@@ -518,14 +488,14 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                         lim_min = min(lim_min, lim[q]);
                     }
                 }
-                if (!dry) mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
+                mbar_wait(&ms.s_full[sb], g / 2, abort_flag);
                 tc_fence_after();
                 float s[N];
 #pragma unroll
                 for (int c0 = 0; c0 < N; c0 += 16) tmem_ld16(tmem + lane_base + L::TMEM_S + sb * N + c0, s + c0);
                 tmem_wait_ld();
                 tc_fence_before();
-                if (!dry) mbar_arrive(&ms.s_empty[sb]);
+                mbar_arrive(&ms.s_empty[sb]);
 
                 // x = log2-domain exponent of the stored probability: score*scale - m_ref + P_SCALE_LOG2
                 const int pos = tid < TILE ? pos_first + tid : 0x7fffffff;           // lanes beyond the tile: always masked
@@ -540,11 +510,11 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                 float xm = x[0];
 #pragma unroll
                 for (int c = 1; c < N; ++c) xm = fmaxf(xm, x[c]);
-                const bool recenter = named_bar_or(1, 128, dry || xm > P_SCALE_LOG2 + RECENTER);
+                const bool recenter = named_bar_or(1, 128, xm > P_SCALE_LOG2 + RECENTER);
                 uint8_t* pbuf = smem + L::OFF_P + sb * L::P_BUF_BYTES;
                 if (recenter) {
                     // this tile's P buffer (free once PV(g-2) has completed) is the scratch area of the column reduction
-                    if (!dry) mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
+                    mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
                     float mx[N];
 #pragma unroll
                     for (int c = 0; c < N; ++c) mx[c] = (masked_tile && pos >= lim[c / 16]) ? -INFINITY : s[c] * score_scale;
@@ -583,7 +553,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     }
                 }
                 // P(g) may overwrite its buffer once PV(g-2) has completed
-                if (!dry) mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
+                mbar_wait(&ms.p_empty[sb], g / 2 - 1, abort_flag);
 #pragma unroll
                 for (int c0 = 0; c0 < N; c0 += 16) {
                     uint32_t hi[4], lo[4];
@@ -605,7 +575,7 @@ __global__ void __launch_bounds__(Layout<N>::THREADS, 1) mla_decode_sm100_kernel
                     *reinterpret_cast<uint4*>(pbuf + ((N + c0) / 16) * (MMA_M * 16) + tid * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
                 fence_proxy_async();
-                if (!dry) mbar_arrive(&ms.p_full[sb]);
+                mbar_arrive(&ms.p_full[sb]);
 
                 if (last) {
                     // ---- epilogue of this (CTA, sequence) pair: wait for its last PV, normalise, write out
