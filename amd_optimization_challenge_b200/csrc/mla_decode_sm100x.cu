@@ -53,15 +53,13 @@ struct Cfg {
     // with transform warps the gather role only moves Q and rope bytes; N = 32 runs 3 warps per scheduler either
     // way (registers are handed out per scheduler), so a hybrid cache's rope gather gets the two spare warps
     static constexpr int PW = XF ? 1 : (N == 16 ? 8 : 4);
-    static constexpr int XW = XF ? ((N != 64 && (N == 16 || (ROPE_SEP && !QSPLIT))) ? 8 : 4) : 0;
-    static constexpr int PRODUCERS = 32 * PW, XT = 32 * XW;
+    static constexpr int PRODUCERS = 32 * PW;
     // N = 64: two softmax warpgroups of 128 threads, each with 32 of the 64 query rows (warps w and w + 4 reach the same
     // TMEM lanes), so that a tile is gathered, converted and multiplied once for 64 rows with the softmax cost of 32.
     static constexpr int SMG = N == 64 ? 2 : 1;                   // softmax warpgroups
     static constexpr int NC = N / SMG;                            // query rows (S / O columns) per softmax thread
     static constexpr int SW = 4 * SMG;                            // softmax warps; warp SW issues the MMAs
     static constexpr int FIRST_PRODUCER = 32 * (SW + 1);
-    static constexpr int THREADS = FIRST_PRODUCER + PRODUCERS + XT;
     // N = 64: P_hi and P_lo are two k-steps into the SAME O columns (O = 4 x N columns; with them side by side O alone
     // would fill the 512 TMEM columns), P_lo is then stored unscaled, and P is single buffered (shared memory).
     static constexpr bool MERGED = N == 64;
@@ -78,8 +76,15 @@ struct Cfg {
     static constexpr int P_BUF_BYTES = P_CHUNKS * TILE * 16;
     static constexpr int MISC_RESERVE = 4096;                     // Misc + the tile prefix of ~700 sequences
     static constexpr int FIXED = NS * STAGE_BYTES + Q_BYTES + P_BUFS * P_BUF_BYTES + MISC_RESERVE;
-    // Landing buffers of the transform warps: S per warp, private to it
+    // Landing buffers of the transform warps: S per warp, private to it.  The 16-token units of the tile stream go to
+    // the transform warps round robin, so any number of them works: as many as have a landing buffer, eight at most
+    // (32 rows: five or six instead of four, 2.8 % on the 131072-key shape); four for 64 rows, where six were
+    // measured 6 % slower (the two softmax warpgroups already fill the schedulers).
     static constexpr int RB_FIT = XF ? (SMEM_LIMIT - FIXED) / UNIT_BYTES : 0;
+    static constexpr int XW_MAX = (N == 16 || (N == 32 && ROPE_SEP && !QSPLIT)) ? 8 : (N == 64 ? 4 : 6);
+    static constexpr int XW = !XF ? 0 : (RB_FIT < XW_MAX ? RB_FIT : XW_MAX);
+    static constexpr int XT = 32 * XW;
+    static constexpr int THREADS = FIRST_PRODUCER + PRODUCERS + XT;
     static constexpr int S = !XF ? 0 : (RB_FIT >= 2 * XW ? 2 : 1);
     static constexpr int RB = XW * S;
     static constexpr int OFF_Q = NS * STAGE_BYTES;
@@ -92,10 +97,12 @@ struct Cfg {
     // rows of a stage handed back to the transform warps after each PV token step instead of after the whole PV:
     // worth 2-4 % for the pure MXFP4 cache; not for the hybrid one, whose rope gather waits for the whole stage anyway
     static constexpr bool ROWS_EARLY = XF && !ROPE_SEP;
-    static constexpr int KV_FULL_COUNT = XF ? 32 * XW + (ROPE_SEP ? PRODUCERS : 0) : PRODUCERS;
+    // a transform warp arrives once per unit it has stored (eight units per tile, whoever stores them)
+    static constexpr int KV_FULL_COUNT = XF ? 32 * (TILE / UNIT_TOK) + (ROPE_SEP ? PRODUCERS : 0) : PRODUCERS;
     static_assert(TMEM_NEED <= 512, "TMEM columns");
     static_assert(N != 64 || !QSPLIT, "64 rows per CTA: e4m3 Q only");
-    static_assert(!XF || RB_FIT >= XW, "landing buffers");
+    static_assert(!XF || (XW >= 1 && RB_FIT >= XW), "landing buffers");
+    static_assert(THREADS <= 512 || N != 64, "the 64-row variant needs 128 registers per thread");
     static_assert((UNIT_TOK * NB) % 32 == 0 && UNIT_BYTES % 16 == 0, "unit layout");
 };
 
@@ -447,7 +454,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             }
         } else if (C::XF && warp >= C::SW + 1 + C::PW) {
             // =========================== transform (block-scaled caches) ===========================
-            // Warp xw owns the 16-token units xw, xw + XW, ... of every tile and S private landing buffers.  For each
+            // The CTA's tiles are a stream of 16-token units (eight per tile); warp xw owns units xw, xw + XW, ... of
+            // that stream (round robin, so XW need not divide eight) and S private landing buffers.  For each
             // unit it fetches the raw rows itself (16-byte cp.async of the codes, the aligned 8-byte words around the
             // E8M0 bytes; rows past the end of the sequence are zero filled), moves a landed unit into registers,
             // reuses the buffer for the unit S ahead at once, and then turns 32-code blocks into pairs of 16-byte
@@ -455,17 +463,17 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             // same column of eight consecutive rows, which the swizzle spreads over all banks, and reads eight rows
             // whose padded pitch does the same.  Each unit has its own exponent frame: its largest E8M0 byte.
             constexpr int NBH = C::NB / 2;                                // blocks per lane per unit
-            constexpr int UPW = (TILE / UNIT_TOK) / (C::XW > 0 ? C::XW : 1);   // units per warp per tile
+            constexpr int UNITS = TILE / UNIT_TOK, XWN = C::XW > 0 ? C::XW : 1;   // units per tile; stride of this warp's units
             constexpr int S = C::S > 0 ? C::S : 1;
             constexpr int CODE_IT = UNIT_TOK * C::NB / 32, PER = CODE_IT + 2;   // copy instructions per lane per unit: codes, E8M0 words
             const int xw = warp - C::SW - 1 - C::PW;
             const int tok = lane & (UNIT_TOK - 1), par = lane >> 4;
-            const int J = n_total * UPW;                                  // units of this warp
+            const int J = (n_total * UNITS - xw + XWN - 1) / XWN;         // units of this warp (xw < UNITS <= n_total * UNITS)
             Walker wn; wn.init(prefix, p.batch, t_begin);
             // cache slot of row `tok` of this warp's unit j; -1 past the end of the sequence or of the span
             auto fetch_slot = [&](int j) -> int {
                 if (j >= J) return -1;
-                const int g = j / UPW, k = xw + (j - g * UPW) * C::XW;
+                const int u = xw + j * XWN, g = u / UNITS, k = u - g * UNITS;
                 wn.seek(p, prefix, t_begin + g);
                 const int pos = (t_begin + g - wn.seq_t0) * TILE + k * UNIT_TOK + tok;
                 return pos < wn.seq_len ? (int)slot_of(p, wn.b, wn.seq_base, wn.page_base, pos) : -1;
@@ -511,7 +519,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
             }
             int nxt2 = fetch_slot(S + 1);                                 // page-table entries are read two units ahead of their use
             for (int j = 0; j < J; ++j) {
-                const int g = j / UPW, ku = j - g * UPW, k = xw + ku * C::XW, st = g % NS, buf = j % S;
+                const int u = xw + j * XWN, g = u / UNITS, k = u - g * UNITS, st = g % NS, buf = j % S;
                 cp_async_wait_pending<S - 1>();                           // this lane's copies of unit j have landed
                 __syncwarp();                                             // ... and every other lane's
                 const unsigned char* unit = smem + C::OFF_RAW + (xw * S + buf) * C::UNIT_BYTES;
@@ -553,7 +561,7 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                 }
                 // this unit's rows of the stage are free (the whole stage where the rows are not released one by one)
                 if (C::ROWS_EARLY) mbar_wait(&ms.kv_rows_free[st][k / 2], g / NS - 1, abort_flag);
-                else if (ku == 0) mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
+                else mbar_wait(&ms.kv_empty[st], g / NS - 1, abort_flag);
                 if (lane == 0) ms.tile_exp[st][k] = e_unit;
                 unsigned char* dst_lat = smem + st * STAGE_BYTES + k * (UNIT_TOK * 128);   // panels 0-3: 128-byte rows
                 unsigned char* dst_rope = smem + st * STAGE_BYTES + k * (UNIT_TOK * 64);   // rope panel: 64-byte rows
@@ -564,10 +572,8 @@ __global__ void __launch_bounds__(Cfg<N, KVFMT, QFMT>::THREADS, 1) mla_decode_sm
                     *reinterpret_cast<uint4*>(d) = ob[PIN ? 2 * i : 0];
                     *reinterpret_cast<uint4*>(reinterpret_cast<uintptr_t>(d) ^ 16) = ob[PIN ? 2 * i + 1 : 1];
                 }
-                if (ku == UPW - 1) {
-                    fence_proxy_async();                                  // the MMA reads the tile through the async proxy
-                    mbar_arrive(&ms.kv_full[st]);
-                }
+                fence_proxy_async();                                      // the MMA reads the tile through the async proxy
+                mbar_arrive(&ms.kv_full[st]);                             // one arrival per lane and unit
             }
             cp_async_wait_all();
             if (bad_page && blockIdx.y == 0) atomicOr(p.status, (int)ST_BAD_PAGE);
@@ -944,8 +950,17 @@ cudaError_t dispatch_formats(const MlaParams& p, int* status, cudaStream_t strea
 // 64 query rows per CTA where the format pair has that variant (a tile is then gathered and converted once per 64
 // rows), else 32 or 16.
 int sm100x_rows_per_cta(const MlaParams& p) {
-    if (p.rows % 64 == 0 && p.q_format == Q_E4M3 && p.kv_format != KV_E4M3) return 64;
-    return p.rows % 32 == 0 ? 32 : 16;
+    // the widest variant whose shared-memory layout (it ends with the tile prefix of the batch) fits
+    bool fits = false;
+    if (p.rows % 64 == 0 && p.q_format == Q_E4M3 && p.kv_format != KV_E4M3) {
+        dispatch_formats<64>(p, nullptr, nullptr, true, &fits);
+        if (fits) return 64;
+    }
+    if (p.rows % 32 == 0) {
+        dispatch_formats<32>(p, nullptr, nullptr, true, &fits);
+        if (fits) return 32;
+    }
+    return 16;
 }
 
 // Every format pair except e4m3 Q x e4m3 cache; the tile-prefix table must fit beside the rings.
