@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(128) peer_merge_kernel(const PeerMergeParams p
     // 1. signal (one CTA), 2. wait (every CTA, one thread per peer)
     if (tid < W) {
         if (blockIdx.x == 0) {
-            __threadfence_system();
+            // release at system scope: the partial was written by earlier kernels of this stream (visible device-wide at
+            // the kernel boundary); the release orders it before the flag for the peers as well
             st_release_sys(reinterpret_cast<unsigned int*>(const_cast<char*>(p.base[tid])) + p.rank, p.epoch);
         }
         const unsigned int* mine = reinterpret_cast<const unsigned int*>(p.base[p.rank]) + tid;
