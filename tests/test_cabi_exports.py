@@ -29,21 +29,25 @@ def test_header_symbols_are_exported(built_lib):
 
 
 def test_struct_layout_matches_header(built_lib, tmp_path):
-    from amd_optimization_challenge_b200._cabi import DecodeArgs
-    fields = [f[0] for f in DecodeArgs._fields_]
-    body = "\n".join('    printf("%s %%zu\\n", offsetof(b200_mla_decode_args, %s));' % (f, f) for f in fields)
-    prog = ('#include <stdio.h>\n#include <stddef.h>\n#include "b200_mla.h"\n'
-            'int main(void) {\n    printf("%zu\\n", sizeof(b200_mla_decode_args));\n' + body + '\n    return 0;\n}\n')
+    """Size and every field offset of the three argument structs: the C header against the ctypes mirror."""
+    from amd_optimization_challenge_b200._cabi import DecodeArgs, KvAppendArgs, PeerMergeArgs
+    pairs = (("b200_mla_decode_args", DecodeArgs), ("b200_mla_kv_append_args", KvAppendArgs),
+             ("b200_mla_peer_merge_args", PeerMergeArgs))
+    body = ""
+    for cname, cls in pairs:
+        body += '    printf("%s %%zu\\n", sizeof(%s));\n' % (cname, cname)
+        for f in cls._fields_:
+            body += '    printf("%s.%s %%zu\\n", offsetof(%s, %s));\n' % (cname, f[0], cname, f[0])
+    prog = ('#include <stdio.h>\n#include <stddef.h>\n#include "b200_mla.h"\nint main(void) {\n' + body + '    return 0;\n}\n')
     c = tmp_path / "layout.c"
     c.write_text(prog)
     exe = tmp_path / "layout"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(c), "-o", str(exe)], check=True)
-    lines = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
-    assert int(lines[0]) == ctypes.sizeof(DecodeArgs)
-    for ln in lines[1:]:
-        if ln.strip():
-            name, off = ln.split()
-            assert getattr(DecodeArgs, name).offset == int(off), name
+    got = dict(ln.split() for ln in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n") if ln.strip())
+    for cname, cls in pairs:
+        assert int(got[cname]) == ctypes.sizeof(cls), cname
+        for f in cls._fields_:
+            assert getattr(cls, f[0]).offset == int(got[f"{cname}.{f[0]}"]), f"{cname}.{f[0]}"
 
 
 def test_argument_validation_without_gpu(built_lib):
@@ -63,6 +67,22 @@ def test_argument_validation_without_gpu(built_lib):
     assert lib.b200_mla_quantize_fp8(None, 8, None, None, None, None) == -1
     assert lib.b200_mla_workspace_bytes(0, 16, 1) == 0
     assert lib.b200_mla_workspace_bytes(32, 16, 1) > 32 * 16 * 512 * 4
+    # peer-memory entry points: layout arithmetic and the checks that run before any CUDA call
+    from amd_optimization_challenge_b200._cabi import PeerMergeArgs
+    part = (256 * 513 * 4 + 255) // 256 * 256
+    assert lib.b200_mla_peer_exchange_bytes(256) == 256 + 2 * part and lib.b200_mla_peer_exchange_bytes(0) == 0
+    assert lib.b200_mla_peer_partial_offset(256, 2) == 256 and lib.b200_mla_peer_partial_offset(256, 3) == 256 + part
+    assert lib.b200_mla_peer_merge(None, None) == -1
+    m = PeerMergeArgs(world=3, rank=0, epoch=1, rows=16)
+    assert lib.b200_mla_peer_merge(ctypes.byref(m), None) == -2 and b"world" in lib.b200_mla_last_error()
+    m.world, m.rank = 2, 2
+    assert lib.b200_mla_peer_merge(ctypes.byref(m), None) == -1
+    m.rank, m.epoch = 1, 0
+    assert lib.b200_mla_peer_merge(ctypes.byref(m), None) == -1 and b"epoch" in lib.b200_mla_last_error()
+    m.epoch = 1
+    assert lib.b200_mla_peer_merge(ctypes.byref(m), None) == -1          # bases and out are NULL
+    assert lib.b200_mla_peer_alloc(0, None, None) == -1 and lib.b200_mla_peer_open(None, None) == -1
+    assert lib.b200_mla_peer_close(None) == 0 and lib.b200_mla_peer_free(None) == 0
 
 
 def test_package_fails_loudly_without_library(tmp_path):
