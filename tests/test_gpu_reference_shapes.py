@@ -233,3 +233,48 @@ def test_one_dominant_key_and_a_long_coherent_tail(pkg, impl, kv_format, q_forma
     if gap_log2 >= 15.0:
         v0 = kv[0, 0, :512].float()
         assert (ref[0, 0].float().cpu() - v0).abs().max() > 0.1 * v0.abs().max()
+
+
+def test_repeated_calls_reuse_a_plan_and_notice_every_change(pkg):
+    """custom_kernel keeps what a call worked out (validated tensors, argument struct, scratch) and reuses it when
+    the same tuple comes again, as the harness does.  A reused plan must give the first call's result, and must not
+    survive a change of q, of the cache planes, of kv_indptr or of a config value."""
+    from amd_optimization_challenge_b200 import submission
+    data = pkg.generate_input(3, 1, 300, seed=61, kv_lens=[300, 40, 131], shuffle_pages=True, formats=("fp8", "mxfp4"))
+    q, kvd, qo, kvp, cfg = data
+    first = pkg.custom_kernel(data)
+    again = pkg.custom_kernel(data)
+    third = pkg.custom_kernel(data)
+    torch.cuda.synchronize()
+    assert (id(cfg), id(kvd)) in submission._plans
+    assert torch.equal(first, again) and torch.equal(first, third) and again.data_ptr() != first.data_ptr()
+    assert_close(first, oracle_for_data(data, "fp8", "fp8"), tight=1.5e-2)
+    # new q object, same config and caches
+    q2 = (q.float() * 0.5 + 0.1).to(torch.bfloat16)
+    out2 = pkg.custom_kernel((q2, kvd, qo, kvp, cfg))
+    torch.cuda.synchronize()
+    assert_close(out2, oracle_for_data((q2, kvd, qo, kvp, cfg), "fp8", "fp8"), tight=1.5e-2)
+    # q rewritten in place: same plan, new contents
+    q2.copy_(q)
+    out3 = pkg.custom_kernel((q2, kvd, qo, kvp, cfg))
+    torch.cuda.synchronize()
+    assert torch.equal(out3, first)
+    # config changed in place: the other cache of the same tuple
+    cfg["kv_format"] = "mxfp4"
+    out4 = pkg.custom_kernel((q2, kvd, qo, kvp, cfg))
+    out5 = pkg.custom_kernel((q2, kvd, qo, kvp, cfg))
+    torch.cuda.synchronize()
+    assert torch.equal(out4, out5)
+    assert_close(out4, oracle_for_data((q2, kvd, qo, kvp, cfg), "mxfp4", "bf16"), tight=1.5e-2)
+    cfg.pop("kv_format")
+    # a cache plane replaced inside the same dict
+    codes, scale = kvd["fp8"]
+    kvd["fp8"] = (codes.clone(), scale)
+    out6 = pkg.custom_kernel((q2, kvd, qo, kvp, cfg))
+    torch.cuda.synchronize()
+    assert torch.equal(out6, first)
+    # a different kv_indptr (shorter second sequence): the result must follow it
+    kvp2 = kvp.clone()
+    out7 = pkg.custom_kernel((q2, kvd, qo, kvp2, cfg))
+    torch.cuda.synchronize()
+    assert torch.equal(out7, first)
