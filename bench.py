@@ -313,7 +313,10 @@ def sharded_modes(pkg, dist, rank, world, dev, kernel="auto", steps=30):
                             "floor_us": (world - 1) * dec.n * 4 / 770e9 * 1e6,
                             "frac": ((world - 1) * dec.n * 4 / 770e9 * 1e6) / max(float(pm_min[0]), 1e-9)}, "speedup_vs_n1": t1 / tp, "efficiency_vs_n1": t1 / tp / world,
         "speedup_vs_all_gather_mode": tn / tp, "max_abs_diff_vs_all_gather_mode": float(diff[0]),
-        "status_bits_max_rank": int(st[0])}
+        "status_bits_max_rank": int(st[0]),
+        # the same partials merged by the same arithmetic: anything but an identical output and a clean status word
+        # means the exchange went wrong, and the timings above are then not a result
+        "valid": bool(float(diff[0]) == 0.0 and int(st[0]) == 0)}
     pdec.close()
     return out
 
