@@ -81,7 +81,9 @@ typedef struct {
 
     /* ---- KV cache planes (device) ---- */
     const void *kv_codes;     /* e4m3: [slots,576]; mxfp4: [slots,288]; hybrid: latent [slots,256] */
-    int64_t kv_codes_stride;  /* bytes between slots; multiple of 16 */
+    int64_t kv_codes_stride;  /* bytes between slots; multiple of 16.  e4m3 caches: a 16-byte aligned plane is fetched by the
+                               * copy engine (TMA: tiled boxes without a page table, four-row gathers by page id with one);
+                               * an unaligned one by 16-byte copies, with the same result */
     const void *kv_block_scales;   /* E8M0 bytes (mxfp4: >=18 per slot, hybrid: >=16); NULL for e4m3.  The tcgen05
                                     * kernels fetch a slot's bytes as the aligned 8-byte words around them: up to 7
                                     * bytes before the first and after the last row of the plane may be read
